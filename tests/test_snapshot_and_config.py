@@ -118,12 +118,62 @@ def test_snapshot_round_trip(tmp_path):
                 want = rows
         assert torch.equal(rows, want)
     # corrupt one byte: verification must fail
-    f = os.path.join(path, "owner_0", "mla_000.bin")
+    f = os.path.join(path, "owner_000", "request_00000.mla_000.bin")
     raw = bytearray(open(f, "rb").read())
     raw[10] ^= 0xFF
     open(f, "wb").write(bytes(raw))
     with pytest.raises(ValueError):
-        SnapshotReader(path, verify_payload=True)
+        SnapshotReader(path).verify()
+    with pytest.raises(ValueError):            # payload verification is the default of a restore
+        cache_io.restore(ula.init(spec, LocalCacheBindings(device="cpu")), path, new_req)
+    # a committed directory is never written into again, and cannot be committed twice
+    with pytest.raises(FileExistsError):
+        cache_io.save_shard(cache, path, layout, reqs, req_ids, 0)
+    with pytest.raises(FileExistsError):
+        finalize_snapshot(path)
+
+
+def _write_owner_shard(args):
+    path, owner, keys = args
+    from ulacache_b200.tools.snapshot.format import SnapshotLayout, SnapshotRequest, SnapshotWriter
+
+    layout = SnapshotLayout("m", owners=4, layers=3, mla_row_bytes=16, index_anchors=(0,), index_segment_bytes=(8, 4))
+    reqs = [SnapshotRequest(k, tuple(range(37 + i)), (5,)) for i, k in enumerate(keys)]
+    w = SnapshotWriter(path, layout, reqs, owner)
+    for req in reqs:
+        for plane, width in layout.planes().items():
+            rows = req.owned_rows(owner, layout.owners)
+            w.write_plane(req.key, plane, [bytes([owner]) * (rows * width)])
+    return w.finish()["metadata_sha256"]
+
+
+def test_snapshot_owners_write_in_parallel_processes_and_disagreement_is_refused(tmp_path):
+    import multiprocessing as mp
+
+    from ulacache_b200.tools.snapshot.format import SnapshotWriter
+
+    path = str(tmp_path / "par")
+    ctx = mp.get_context("spawn")
+    with ctx.Pool(4) as pool:
+        hashes = pool.map(_write_owner_shard, [(path, o, ("a", "b", "c")) for o in range(4)])
+    assert len(set(hashes)) == 1
+    commit = finalize_snapshot(path)
+    assert commit["request_count"] == 3 and sorted(commit["owners"]) == ["0", "1", "2", "3"]
+    r = SnapshotReader(path)
+    assert r.verify()["verified_bytes"] == sum(os.path.getsize(os.path.join(path, f"owner_{o:03d}", n))
+                                               for o in range(4) for n in os.listdir(os.path.join(path, f"owner_{o:03d}"))
+                                               if n.endswith(".bin"))
+    assert b"".join(r.iter_plane(2, "b", "index_000")) == bytes([2]) * (r.plane_rows(2, "b") * 12)
+    # an owner that saved the requests under other keys (same sizes, other metadata) is refused at commit
+    bad = str(tmp_path / "bad")
+    for o in (0, 1, 2):
+        _write_owner_shard((bad, o, ("a", "b", "c")))
+    _write_owner_shard((bad, 3, ("a", "c", "b")))
+    with pytest.raises(ValueError):
+        finalize_snapshot(bad)
+    # the same owner cannot write twice into one snapshot directory
+    with pytest.raises(FileExistsError):
+        _write_owner_shard((bad, 0, ("a", "b", "c")))
 
 
 def test_every_shipped_model_configuration_loads():

@@ -17,17 +17,17 @@ def main(argv=None) -> int:
     ap.add_argument("path")
     args = ap.parse_args(argv)
     if args.command == "commit":
-        meta = finalize_snapshot(args.path)
-        print(json.dumps({"committed": True, "files": len(meta["files"])}))
+        commit = finalize_snapshot(args.path)
+        print(json.dumps({"committed": True, "owners": len(commit["owners"]), "requests": commit["request_count"]}))
         return 0
     reader = SnapshotReader(args.path, require_committed=args.command == "verify", verify_payload=False)
     if args.command == "verify":
-        print(json.dumps({"verified_bytes": reader.verify()}))
+        print(json.dumps(reader.verify()))
         return 0
     lay = reader.layout
-    print(json.dumps({"committed": bool(reader.meta.get("committed")), "owners": lay.owners, "layers": lay.layers,
+    print(json.dumps({"committed": reader.committed, "owners": lay.owners, "layers": lay.layers,
                       "kv_format": lay.kv_format, "mla_row_bytes": lay.mla_row_bytes,
-                      "index_layers": list(lay.index_layers), "requests": len(reader.requests),
+                      "index_anchors": list(lay.index_anchors), "requests": len(reader.requests),
                       "tokens": sum(r.next_position for r in reader.requests)}))
     return 0
 

@@ -44,7 +44,7 @@ def save_shard(cache, path: str, layout: SnapshotLayout, requests: Sequence[Snap
                         yield rows.cpu().numpy().tobytes()
 
                 writer.write_plane(req.key, plane, chunks())
-        for layer in layout.index_layers:
+        for layer in layout.index_anchors:
             plane = f"index_{layer:03d}"
             for req in requests:
                 ids = request_ids[req.key][: req.next_position][owner::layout.owners]
@@ -70,15 +70,20 @@ def restore(cache, path: str, request_ids: Dict[str, object], *, verify_payload=
                 ids = request_ids[req.key][: req.next_position][owner::lay.owners]
                 if ids.numel() == 0:
                     continue
+                rows = reader.plane_rows(owner, req.key)
                 for layer in range(lay.layers):
                     plane = f"mla_{layer:03d}"
-                    off, rows = reader.request_range(owner, plane, req.key)
-                    src = FileRecordSource(reader.plane_file(owner, plane), off, rows, lay.mla_row_bytes, lay.kv_format)
+                    if reader.verify_payload:
+                        reader.verify_plane(owner, req.key, plane)      # hash before any record reaches the cache
+                    else:
+                        reader.validate_owner(owner)
+                    src = FileRecordSource(reader.plane_file(owner, req.key, plane), 0, rows, lay.mla_row_bytes,
+                                           lay.kv_format)
                     done += cache.write(ids, layer, src)
-                for layer in lay.index_layers:
+                for layer in lay.index_anchors:
                     if index_writer is None:
                         continue
                     plane = f"index_{layer:03d}"
-                    data = b"".join(reader.iter_plane(owner, plane, req.key))
+                    data = b"".join(reader.iter_plane(owner, req.key, plane))
                     index_writer(layer, ids, data)
     return done
