@@ -39,5 +39,32 @@ def time_cuda(fn, *, warmup=3, iters=10):
     return e0.elapsed_time(e1) / iters * 1e3        # microseconds per call
 
 
+def time_cuda_graph(fn, *, warmup=2, iters=12, replays=3):
+    """Microseconds of DEVICE time per call: ``iters`` calls are captured into one CUDA graph and the
+    graph is replayed, so host launch cost (which exceeds the device time of small kernels) does not
+    count.  ``fn`` must be capture-safe (no synchronisation; it may allocate through torch)."""
+    import torch
+
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    stream = torch.cuda.Stream()
+    stream.wait_stream(torch.cuda.current_stream())
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph, stream=stream):
+        for _ in range(iters):
+            fn()
+    torch.cuda.synchronize()
+    graph.replay()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(replays):
+        graph.replay()
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) / (iters * replays) * 1e3
+
+
 def emit(**kw):
     print(json.dumps(kw), flush=True)

@@ -9,7 +9,40 @@ from __future__ import annotations
 
 import argparse
 
-from .common import emit, measured_peaks, time_cuda
+from .common import emit, measured_peaks, time_cuda, time_cuda_graph
+
+
+def dense_sweep(args):
+    """Input projection (7168 -> 2304), q_b + indexer q (1536 -> 32768) and o_proj (16384 -> 7168) with
+    the row counts of decode; device time per launch (weights rotate over copies, so they come from HBM)."""
+    import torch
+    from ..ops import fp8
+
+    dev = "cuda"
+    peaks = measured_peaks()
+    for (name, Nout, K) in [("w_in", 2304, 7168), ("w_qb", 32768, 1536), ("w_o", 7168, 16384)]:
+        ws = [fp8.random_fp8_weight((Nout, K), device=dev) for _ in range(6)]
+        for M in (32, 64):
+            x8, sx = fp8.act_quant(torch.randn(M, K, device=dev, dtype=torch.bfloat16))
+            for rows_hint in (16, 32, 64):
+                if rows_hint > M:
+                    continue
+                for splits in sorted({1, 2, 4, 8, 16, fp8.pick_splits(Nout, K)}):
+                    if splits > K // 128:
+                        continue
+                    i = [0]
+
+                    def run():
+                        q, s = ws[i[0] % 6]
+                        i[0] += 1
+                        fp8.grouped_gemm(x8, sx, q, s, splits=splits, max_rows=rows_hint)
+
+                    us = time_cuda_graph(run, iters=12)
+                    gbs = Nout * K / us / 1e3
+                    emit(kernel="fp8_grouped_gemm", case=f"{name} {Nout}x{K}", M=M, rows_hint=rows_hint, splits=splits,
+                         picked=splits == fp8.pick_splits(Nout, K), us=round(us, 1), gb_per_s=round(gbs, 1),
+                         frac_of_hbm_peak=round(gbs / peaks["hbm_gbs"], 3))
+        del ws
 
 
 def main():
@@ -19,7 +52,11 @@ def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--small", action="store_true")
     ap.add_argument("--iters", type=int, default=10)
+    ap.add_argument("--dense-sweep", action="store_true",
+                    help="the dense projections of one decoder layer at 32 and 64 rows: every K split and ring geometry")
     args = ap.parse_args()
+    if args.dense_sweep:
+        return dense_sweep(args)
     dev = "cuda"
     peaks = measured_peaks()
     torch.manual_seed(0)

@@ -253,6 +253,7 @@ def main(argv=None):
     ap.add_argument("--out", default="")
     ap.add_argument("--rows", default="8,32,64,128,256")
     ap.add_argument("--ctx", default="32768,65536,131072")
+    ap.add_argument("--only", default="", help="comma list of arms to run: topk, index_key_store, exchange (default all)")
     ap.add_argument("--small", action="store_true", help="one small case per kernel (first contact with a new box)")
     args = ap.parse_args(argv)
     try:
@@ -268,11 +269,15 @@ def main(argv=None):
     timer = _Timer(torch.device("cuda"))
     rows = [8] if args.small else [int(x) for x in args.rows.split(",")]
     ctx = [32768] if args.small else [int(x) for x in args.ctx.split(",")]
+    only = {x for x in args.only.split(",") if x}
     report = {"gpu": torch.cuda.get_device_name(0),
-              "timing": "CUDA events, median of 10 after 3 warm-up calls, 256 MB L2 flush before each",
-              "topk": bench_topk(mods, timer, rows, ctx),
-              "index_key_store": bench_index_store(mods, timer, [32] if args.small else [32, 2048, 32768]),
-              "host_to_hbm_exchange": bench_exchange(mods, timer, [2048] if args.small else [2048, 65536])}
+              "timing": "CUDA events, median of 10 after 3 warm-up calls, 256 MB L2 flush before each"}
+    if not only or "topk" in only:
+        report["topk"] = bench_topk(mods, timer, rows, ctx)
+    if not only or "index_key_store" in only:
+        report["index_key_store"] = bench_index_store(mods, timer, [32] if args.small else [32, 2048, 32768])
+    if not only or "exchange" in only:
+        report["host_to_hbm_exchange"] = bench_exchange(mods, timer, [2048] if args.small else [2048, 65536])
     text = json.dumps(report, indent=1)
     if args.out:
         with open(args.out, "w") as fh:

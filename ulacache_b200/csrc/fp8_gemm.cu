@@ -18,6 +18,7 @@
 // The reference library has no GEMM; the serving framework it patches uses
 // DeepGEMM for this role.
 #include <stdlib.h>
+#include "ulc/launch.h"
 #include "ulc/ptx.cuh"
 #include "ulc/tmap.h"
 
@@ -77,6 +78,18 @@ struct F8Barriers {
   uint32_t tmem_base;
   int abort_flag;
 };
+
+// Optional timeline of CTA 0, compiled in with -DULC_F8_TRACE (development only):
+// f8_trace[role][slot][event] = clock64; roles: 0 producer, 1 first MMA issuer, 2 epilogue group 0.
+#ifdef ULC_F8_TRACE
+__device__ long long f8_trace[3][64][4];
+#define F8_T(role, slot, ev)                                                                   \
+  do {                                                                                         \
+    if (blockIdx.x == 0 && (slot) < 64) f8_trace[role][slot][ev] = clock64();                   \
+  } while (0)
+#else
+#define F8_T(role, slot, ev) do {} while (0)
+#endif
 
 struct F8Item {
   int e, n0, kb0, nkb, m_begin, m_end;
@@ -147,6 +160,7 @@ fp8_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid
         const F8Item w = f8_item(p, idx);
         const int tokens = w.m_end - w.m_begin;
         const int passes = tokens > 0 ? (tokens + kF8MaxN - 1) / kF8MaxN : 0;
+        F8_T(0, (idx - blockIdx.x) / gridDim.x, 0);          // producer reaches this item
         for (int ps = 0; ps < passes && !*abort_flag; ++ps) {
           const int t0 = w.m_begin + ps * kF8MaxN;
           const int nt = min(kF8MaxN, w.m_end - t0);
@@ -167,6 +181,7 @@ fp8_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid
             issued = it + 1;
           }
         }
+        F8_T(0, (idx - blockIdx.x) / gridDim.x, 1);          // ... has issued its last load
       }
       if (*abort_flag)
         for (int i = max(0, issued - kF8Stages); i < issued; ++i)
@@ -183,6 +198,7 @@ fp8_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid
         const F8Item w = f8_item(p, idx);
         const int tokens = w.m_end - w.m_begin;
         const int passes = tokens > 0 ? (tokens + kF8MaxN - 1) / kF8MaxN : 0;
+        if (mma_id == 0) F8_T(1, (idx - blockIdx.x) / gridDim.x, 0);   // issuer reaches this item
         for (int ps = 0; ps < passes && !*abort_flag; ++ps) {
           const int nt = min(kF8MaxN, w.m_end - (w.m_begin + ps * kF8MaxN));
           const uint32_t n_mma = static_cast<uint32_t>((nt + 15) / 16 * 16);
@@ -207,6 +223,7 @@ fp8_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid
             ptx::umma_commit(&bar.acc_full[ab]);
           }
         }
+        if (mma_id == 0) F8_T(1, (idx - blockIdx.x) / gridDim.x, 1);   // ... has issued its last MMA
       }
     }
   } else {
@@ -228,6 +245,7 @@ fp8_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid
       const int tokens = w.m_end - w.m_begin;
       const int passes = tokens > 0 ? (tokens + kF8MaxN - 1) / kF8MaxN : 0;
       const int f = w.n0 + qd * 32 + lane;           // output feature of this thread
+      if (etid == 0) F8_T(2, (idx - blockIdx.x) / gridDim.x, 0);       // epilogue reaches this item
       const float* sw_tile = p.sw + (static_cast<size_t>(w.e) * (p.Nout / kF8BM) + w.n0 / kF8BM) * KB + w.kb0;
       for (int ps = 0; ps < passes && !*abort_flag; ++ps) {
         const int t0 = w.m_begin + ps * kF8MaxN;
@@ -245,6 +263,7 @@ fp8_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid
             s_scale[j * kF8MaxKB + i] = j < nt ? sx_base[static_cast<size_t>(j) * KB + i] * sw_tile[i] : 0.f;
           }
           asm volatile("bar.sync 3, 256;" ::: "memory");
+          if (etid == 0) F8_T(2, (idx - blockIdx.x) / gridDim.x, 1);   // scale table ready
         }
         // (wide geometries) scales of the first 16 tokens are fetched one turn ahead of their use
         float s_pref[16];
@@ -310,6 +329,7 @@ fp8_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid
           if (lane == 0) ptx::mbar_arrive(&bar.acc_empty[ab]);
         }
         if (*abort_flag) break;
+        if (etid == 0) F8_T(2, (idx - blockIdx.x) / gridDim.x, 2);     // last K block consumed
         if (kAlternate) {
           // group 1 parks its partial sums, group 0 adds them and stores
           const int row = qd * 32 + lane;
@@ -345,6 +365,7 @@ fp8_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid
             }
           }
         }
+        if (etid == 0) F8_T(2, (idx - blockIdx.x) / gridDim.x, 3);     // stored
       }
     }
   }
@@ -419,13 +440,9 @@ static int make_w_tmap(CUtensorMap* out, const void* w, int E, int Nout, int K) 
 
 template <int MAXN>
 static int launch_f8(const CUtensorMap& tw, const CUtensorMap& tx, const F8Params& p, int grid, cudaStream_t stream) {
-  static bool configured = false;
-  if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(fp8_grouped_gemm_kernel<MAXN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         F8Geom<MAXN>::kSmem);
-    if (e != cudaSuccess) return static_cast<int>(e);
-    configured = true;
-  }
+  static PerDeviceOnce once;
+  const int rc = ensure_dynamic_smem(reinterpret_cast<const void*>(fp8_grouped_gemm_kernel<MAXN>), F8Geom<MAXN>::kSmem, once);
+  if (rc != 0) return rc;
   fp8_grouped_gemm_kernel<MAXN><<<grid, kF8Threads, F8Geom<MAXN>::kSmem, stream>>>(tw, tx, p);
   return static_cast<int>(cudaGetLastError());
 }
@@ -445,6 +462,12 @@ int ulc_fp8_grouped_gemm_peers(const void* x8, const float* sx, const void* w8, 
                                int M, int Nout, int K, int E, int splits, int max_rows, void* y,
                                void* const* peer_out, int n_peers, int32_t* work, int32_t* status,
                                cudaStream_t stream);
+
+#ifdef ULC_F8_TRACE
+int ulc_f8_trace_read(long long* host) {
+  return static_cast<int>(cudaMemcpyFromSymbol(host, ulc::f8_trace, sizeof(long long) * 3 * 64 * 4));
+}
+#endif
 
 int ulc_fp8_grouped_gemm(const void* x8, const float* sx, const void* w8, const float* sw, const int32_t* offs,
                          int M, int Nout, int K, int E, int splits, int max_rows, void* y, int32_t* work,

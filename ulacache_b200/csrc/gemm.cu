@@ -13,6 +13,7 @@
 // Split-K partial sums go to an fp32 scratch buffer with red.add; a second tiny
 // kernel converts them.  The reference library has no GEMM of its own (it
 // borrows the serving framework's), so this file has no counterpart there.
+#include "ulc/launch.h"
 #include "ulc/ptx.cuh"
 #include "ulc/tmap.h"
 
@@ -182,13 +183,9 @@ static int launch_gemm(const CUtensorMap& tw, const CUtensorMap& tx, void* out, 
                        int splits, int out_mode, int batch, long long ldy, long long y_bstride, int32_t* status,
                        cudaStream_t stream) {
   using S = GemmSmem<BN>;
-  static bool configured = false;
-  if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(gemm_wt_kernel<BN>,
-                                         cudaFuncAttributeMaxDynamicSharedMemorySize, S::kBytes);
-    if (e != cudaSuccess) return static_cast<int>(e);
-    configured = true;
-  }
+  static PerDeviceOnce once;
+  const int attr_rc = ensure_dynamic_smem(reinterpret_cast<const void*>(gemm_wt_kernel<BN>), S::kBytes, once);
+  if (attr_rc != 0) return attr_rc;
   const int total_kb = (K + kGemmBK - 1) / kGemmBK;
   const int kb_per_split = (total_kb + splits - 1) / splits;
   dim3 grid((N + kGemmBM - 1) / kGemmBM, (T + BN - 1) / BN, splits * batch);

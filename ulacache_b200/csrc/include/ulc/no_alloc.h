@@ -16,13 +16,17 @@
 //    library keeps it resident until the process exits.
 //  * splits * B * H * 513 * 4 bytes must fit; larger requests are rejected with
 //    -2 (capacity) and nothing is launched.
-//  * The first call on each device looks up the array's device address
-//    (cudaGetSymbolAddress) with that device current.  Make that first call before
+//  * The first call on EACH device looks up the array's device address
+//    (cudaGetSymbolAddress) and sets the kernel's shared-memory attribute, both with
+//    that device current.  Make that first call, on every device you will use, before
 //    starting any stream capture.
 //  * All calls share the one array and it keeps whatever the previous call left.
-//    Nothing in it has to start at zero: every (split, row) cell is written before
-//    it is read within a call.  Two calls whose kernels overlap on the GPU (other
-//    streams, other threads) race on it; serialise them.
+//    Nothing in it has to start at zero: every (split, row) cell a call reads is
+//    written by that call first.  A CTA that gives up on a bounded wait writes an
+//    empty marker for its cells and reports through the status word; when the status
+//    word is non-zero after a call, `out` and `lse` are undefined.  Two calls whose
+//    kernels overlap on the GPU (other streams, other threads) race on the array;
+//    serialise them.
 //  * No cudaMalloc, cudaFree or allocating library routine is called.
 #pragma once
 #include <cuda_runtime.h>

@@ -22,6 +22,7 @@
 // FlashAG (ulacache/csrc/flashag/b300/ag_kernels_dynamic.cuh:375) followed by a
 // rank-major top-k (ulacache/csrc/indexer/topk_v2.cuh:1467).  Here each rank takes
 // its local top-k and peer-stores only (score, token) candidates.
+#include "ulc/launch.h"
 #include "ulc/layout.h"
 #include "ulc/ptx.cuh"
 #include "ulc/tmap.h"
@@ -211,15 +212,20 @@ index_score_kernel(const __grid_constant__ CUtensorMap tmap_keys, const IndexSco
       const int a = pg0 + 2 * i + pg_in_tile;
 #pragma unroll
       for (int j = 0; j < NQ; ++j) {
-        float acc = 0.f;
+        // both halves of the accumulator row are requested before the first is consumed, and the
+        // weighted sum runs as four independent chains (one chain of 64 dependent FMAs would take
+        // longer than the tile's share of the key stream)
+        uint32_t d0[32], d1[32];
+        ptx::tmem_ld32(tmem + (static_cast<uint32_t>(qd * 32) << 16) + ab * N + j * 64, d0);
+        ptx::tmem_ld32(tmem + (static_cast<uint32_t>(qd * 32) << 16) + ab * N + j * 64 + 32, d1);
+        ptx::tmem_ld_wait();
+        float part[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-        for (int c = 0; c < 64; c += 32) {
-          uint32_t d[32];
-          ptx::tmem_ld32(tmem + (static_cast<uint32_t>(qd * 32) << 16) + ab * N + j * 64 + c, d);
-          ptx::tmem_ld_wait();
-#pragma unroll
-          for (int h = 0; h < 32; ++h) acc = fmaf(sw[j * 64 + c + h], fmaxf(__uint_as_float(d[h]), 0.f), acc);
+        for (int h = 0; h < 32; ++h) {
+          part[h & 3] = fmaf(sw[j * 64 + h], fmaxf(__uint_as_float(d0[h]), 0.f), part[h & 3]);
+          part[h & 3] = fmaf(sw[j * 64 + 32 + h], fmaxf(__uint_as_float(d1[h]), 0.f), part[h & 3]);
         }
+        const float acc = (part[0] + part[1]) + (part[2] + part[3]);
         if (a < pg1)
           p.logits[(static_cast<size_t>(r) * NQ + j) * row_stride + static_cast<size_t>(a) * kPageTokens + off] =
               valid ? acc * kscale : -INFINITY;
@@ -287,13 +293,9 @@ __global__ void candidate_scatter_kernel(const float* __restrict__ vals, const i
 
 template <int NQ>
 static int launch_index_score(const CUtensorMap& tm, const IndexScoreParams& p, dim3 grid, cudaStream_t s) {
-  static bool configured = false;
-  if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(index_score_kernel<NQ>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         IdxGeom<NQ>::kSmem);
-    if (e != cudaSuccess) return static_cast<int>(e);
-    configured = true;
-  }
+  static PerDeviceOnce once;
+  const int rc = ensure_dynamic_smem(reinterpret_cast<const void*>(index_score_kernel<NQ>), IdxGeom<NQ>::kSmem, once);
+  if (rc != 0) return rc;
   index_score_kernel<NQ><<<grid, kIdxThreads, IdxGeom<NQ>::kSmem, s>>>(tm, p);
   return static_cast<int>(cudaGetLastError());
 }

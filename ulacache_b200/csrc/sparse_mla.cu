@@ -24,6 +24,7 @@
 // moves remote rows with record_pull_cached_impl
 // (ulacache/csrc/cache/common.cuh:1037) into a local buffer first; this kernel
 // replaces that pull + the external attention call.
+#include "ulc/launch.h"
 #include "ulc/pool.h"
 #include "ulc/ptx.cuh"
 #include "ulc/tmap.h"
@@ -338,6 +339,10 @@ sparse_mla_decode_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gri
         if (p.splits == 1) { if (p.lse) p.lse[row_index] = lse; }
         else p.part_lse[static_cast<size_t>(split) * p.B * p.H + row_index] = lse;
       }
+    } else if (p.splits > 1 && h < p.H && half == 0) {
+      // A CTA that gave up (a bounded wait expired; the status word says so) still marks its
+      // cells as empty, so that the merge does not read what an earlier call left in the scratch.
+      p.part_lse[static_cast<size_t>(split) * p.B * p.H + static_cast<size_t>(b) * p.H + h] = -INFINITY;
     }
   } else if (warp < kSoftmaxWarps + kMmaIssuers) {
     // =========================================================== MMA issuers ==
@@ -625,12 +630,9 @@ int ulc_sparse_mla_decode_ex(const PoolView* pv, const void* q_lat, long long la
   if (splits > 1 && scratch == nullptr) return -kErrUnsupported;
   if (splits > 1 && (out_sb != static_cast<long long>(H) * 512 || out_sh != 512)) return -kErrUnsupported;
   if ((out_sb & 7) || (out_sh & 7) || (reinterpret_cast<uintptr_t>(out) & 15)) return -kErrAlignment;
-  static bool configured = false;
-  if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(sparse_mla_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kMlaSmem);
-    if (e != cudaSuccess) return static_cast<int>(e);
-    configured = true;
-  }
+  static PerDeviceOnce once;
+  const int attr_rc = ensure_dynamic_smem(reinterpret_cast<const void*>(sparse_mla_decode_kernel), kMlaSmem, once);
+  if (attr_rc != 0) return attr_rc;
   CUtensorMap tq, tr;
   int r = make_q_tmap(&tq, q_lat, B, H, 512, lat_sb, lat_sh);
   if (r != 0) return r;

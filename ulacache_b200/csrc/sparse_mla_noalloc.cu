@@ -1,6 +1,7 @@
 // Sparse MLA decode for callers that may not allocate: the split-KV scratch lives
 // in a file-scope device array of this library.  See ulc/no_alloc.h for who needs
 // this and for the rules of use.
+#include <atomic>
 #include "ulc/no_alloc.h"
 #include "ulc/status.h"
 
@@ -18,7 +19,7 @@ namespace {
 static __device__ __align__(256) unsigned char g_noalloc_scratch[ULC_NOALLOC_SCRATCH_BYTES];
 
 constexpr int kMaxDevices = 64;
-void* g_scratch_addr[kMaxDevices] = {nullptr};
+std::atomic<void*> g_scratch_addr[kMaxDevices];      // zero-initialised; filled once per device, any thread
 
 // Device address of the array on the current device, looked up once per device.
 int scratch_address(void** out) {
@@ -26,13 +27,13 @@ int scratch_address(void** out) {
   cudaError_t e = cudaGetDevice(&dev);
   if (e != cudaSuccess) return static_cast<int>(e);
   if (dev < 0 || dev >= kMaxDevices) return -ulc::kErrUnsupported;
-  if (g_scratch_addr[dev] == nullptr) {
-    void* p = nullptr;
-    e = cudaGetSymbolAddress(&p, g_noalloc_scratch);
+  void* p = g_scratch_addr[dev].load(std::memory_order_acquire);
+  if (p == nullptr) {
+    e = cudaGetSymbolAddress(&p, g_noalloc_scratch);      // threads that race here get the same address
     if (e != cudaSuccess) return static_cast<int>(e);
-    g_scratch_addr[dev] = p;
+    g_scratch_addr[dev].store(p, std::memory_order_release);
   }
-  *out = g_scratch_addr[dev];
+  *out = p;
   return 0;
 }
 

@@ -1,47 +1,61 @@
 // Radix-select top-k (k <= 2048) over rows of fp32 scores.
 //
-// A first pass over the row builds a 2048-bin histogram of the top 11 bits of
-// an order-preserving key.  When the threshold bin is crowded (scores of one
-// request span an octave or two, i.e. a handful of such bins) the cluster
-// kernel histograms the next 11 bits inside it.  The last pass emits everything above
-// the threshold prefix and parks the threshold bin's elements in shared memory,
-// where the remaining bits are refined without touching global memory again.
-// Ties at the k-th value go to the lowest position, so the selected SET is
-// deterministic (the order inside a row is not).
+// Selection works on an order-preserving 32-bit key of the score and proceeds in four steps,
+// all of them over keys that stay in shared memory when the row is short enough (every pass is
+// then a short rolled loop: between two launches of a decode step the instruction lines of a
+// kernel fall out of L2, so the hot path is kept to a few hundred instructions):
 //
-// Two launch shapes:
-//   * one CTA of 1024 threads per row (`topk_row_kernel`), for many rows: two passes over
-//     the row with one shared-memory atomic per element, refinement in shared memory;
-//   * a cluster of kTopkCluster CTAs per row (`topk_kernel<kTopkCluster>`) when there are few
-//     rows: each CTA histograms and emits an interleaved quarter of the row (keys stay in
-//     registers between the passes when the row is short enough), adds its
-//     non-empty bins into every CTA's copy of the summed histogram through
-//     distributed shared memory, stages what it selects locally and claims
-//     its output and candidate ranges from CTA 0 once, and CTA 0 refines alone.
-//     Distributed shared memory is ordinary ld/st/atom on shared::cluster
-//     addresses; no bulk copy is involved.
-// Scores cluster in a few coarse bins (one or two exponents), so in the cluster
-// kernel every counter update is warp-aggregated: lanes that hit the same bin add
-// once (match.any), and output / candidate slots are claimed once per warp.
+//  1. FILTER.  Shared-memory atomics are the scarce resource of a histogram (one lane per
+//     clock), so most elements must never reach one.  A warp sorts 32 sampled keys, eight of them
+//     become candidate cut-offs, every thread counts its keys against the eight (compare + add,
+//     no atomics) and the CTA keeps the highest cut-off that still leaves it 1.5 x its share of
+//     k elements.  Typically 5 - 15 % of a row passes.
+//  2. HISTOGRAM of the survivors over 2048 bins of a WINDOWED key: sign, five exponent bits
+//     covering 2^-15 .. 2^16 (everything outside is clamped into the end bins) and five mantissa
+//     bits, i.e. 32 bins per octave where scores live.  The CTAs of a cluster add their non-empty
+//     bins into every CTA's copy of the row histogram through distributed shared memory; the
+//     histogram is exact from the highest filter bin of the cluster upwards, and the scan for the
+//     k-th element only looks there.  (If it does not find it - a sample that misjudged the row -
+//     the step is redone without a filter.)  A threshold bin with more elements than the
+//     candidate store gets a second 2048-bin level inside it.
+//  3. EMIT.  Keys above the threshold go straight from registers to the output; every warp claims
+//     its range with one atomic, every CTA its range from CTA 0 with one remote atomic.  Keys of
+//     the threshold bin are parked in CTA 0's shared memory.
+//  4. RESOLVE the threshold bin in CTA 0: with few candidates, a candidate is selected iff fewer
+//     than the missing number of candidates beat it (counted by all threads); crowded bins take
+//     radix levels over the 64-bit composite of key and position.
 //
-// Options: per-row lengths, candidate-list input (scores + explicit indices,
-// used for the cross-rank merge), and an index transform through a table
-// (position -> logical record ID).
+// Ties at the k-th value go to the lowest position, so the selected SET is deterministic (the
+// order inside a row is not).
 //
-// Reference counterpart: ulacache/csrc/indexer/topk_v2.cuh:464 (12-bit coarse
-// histogram, register-resident refinement, cluster variant at :1467).  This
-// version keeps candidates in shared memory instead of registers so that one
-// code path serves every row length up to 2^31.
+// Launch shape: a cluster of CS (1, 2, 4 or 8) CTAs of 512 threads per row.  Blocks of 512
+// consecutive elements are dealt to the CTAs of a cluster in turn; a CTA keeps up to 32 blocks of
+// keys in shared memory, so rows up to CS * 512 * 32 elements are read from memory once.
+// Distributed shared memory is ordinary ld / st / red / atom on shared::cluster addresses; no
+// bulk copy is involved.
+//
+// Options: per-row lengths, candidate-list input (scores + explicit indices, used for the
+// cross-rank merge), an index transform through a table or a page table (position -> logical
+// record ID).
+//
+// Reference counterpart: ulacache/csrc/indexer/topk_v2.cuh:464 (fp16-derived 12 / 10-bit coarse
+// histogram of every element, second pass re-reads the row, tie buffer; persistent cluster pool at
+// :547).
+#include "ulc/launch.h"
 #include "ulc/ptx.cuh"
 
 namespace ulc {
 
-constexpr int kTopkThreads = 1024;
+constexpr int kTopkThreads = 512;
+constexpr int kTopkWarps = kTopkThreads / 32;
 constexpr int kTopkBins = 2048;
-constexpr int kTopkCand = 6144;   // shared-memory candidate slots
-constexpr int kTopkSmallBin = 1024;   // a threshold bin above this gets a second histogram level
-constexpr int kTopkCluster = 4;   // CTAs per row in the cluster launch
-constexpr int kTopkRegs = 10;     // blocks of a row whose keys one CTA keeps in registers
+constexpr int kTopkCand = 2048;      // shared-memory candidate slots (elements of the threshold bin)
+constexpr int kTopkRankMax = 512;    // up to this many candidates are resolved by rank counting
+constexpr int kTopkMaxCluster = 8;
+constexpr int kTopkFilters = 8;      // candidate cut-offs of the filter step
+constexpr uint64_t kNoKey = 1ull << 32;   // "above every key"
+// ranks of the sorted sample tried as cut-offs, relative to the expected one
+__constant__ float kTopkRankSpread[kTopkFilters] = {0.6f, 0.85f, 1.15f, 1.5f, 2.f, 3.f, 4.5f, 8.f};
 
 __device__ __forceinline__ uint32_t order_key(float x) {
   uint32_t u = __float_as_uint(x);
@@ -49,18 +63,44 @@ __device__ __forceinline__ uint32_t order_key(float x) {
   return (u & 0x80000000u) ? ~u : (u | 0x80000000u);
 }
 
+// Histogram bin of an order-preserving key: monotone (not strictly) in the key.
+__device__ __forceinline__ uint32_t window_bin(uint32_t key) {
+  const bool nonneg = (key & 0x80000000u) != 0u;
+  const uint32_t mag = (nonneg ? key : ~key) & 0x7fffffffu;        // exponent | mantissa of |x|
+  const int t = static_cast<int>(mag >> 18) - (112 << 5);           // exponent 112 = 2^-15
+  const uint32_t bp = static_cast<uint32_t>(min(max(t, 0), 1023));
+  return nonneg ? 1024u + bp : 1023u - bp;
+}
+
+// Smallest key of bin b (0 .. 2047).  Key 0 is reserved for "no element", so bin 0 starts at 1.
+__device__ __forceinline__ uint32_t bin_lo_key(uint32_t b) {
+  if (b == 0u) return 1u;
+  if (b >= 1024u) {
+    const uint32_t bp = b - 1024u;
+    return 0x80000000u | (bp == 0u ? 0u : ((bp + 3584u) << 18));
+  }
+  // negative scores: the smallest key of the bin belongs to its LARGEST magnitude
+  const uint32_t bp = 1023u - b;
+  const uint32_t mhi = bp == 1023u ? 0x7fffffffu : (((bp + 3585u) << 18) - 1u);
+  return 0x7fffffffu - mhi;
+}
+
 struct TopkShared {
-  uint32_t hist[kTopkBins];
-  uint32_t sum1[kTopkBins];      // cluster launch: level-1 / level-2 histograms summed over the CTAs
-  uint32_t sum2[kTopkBins];
-  uint32_t warp_sums[32];
-  uint32_t cand_key[kTopkCand];
+  uint32_t hist[kTopkBins];      // this CTA's survivors (level 1, then level 2)
+  uint32_t sum[kTopkBins];       // cluster launch: the row, level 1
+  uint32_t sum2[kTopkBins];      // cluster launch: the row, level 2 (inside the threshold bin)
+  uint32_t cand_key[kTopkCand];  // CTA 0: the threshold bin's elements
   int32_t cand_pos[kTopkCand];
-  uint32_t out_count;
-  uint32_t cand_count;
-  uint32_t thr_bin;
-  uint32_t thr_above;
-  uint32_t thr_count;
+  uint32_t warp_sums[32];
+  uint32_t sample[32];
+  uint32_t filt_key[kTopkFilters];
+  uint32_t filt_count[kTopkFilters];
+  uint32_t filt_bin[kTopkMaxCluster];   // filter bin of every CTA of the cluster (written by the peers)
+  uint32_t out_count;            // CTA 0: output slots handed out
+  uint32_t cand_count;           // CTA 0: candidate slots handed out
+  uint32_t local_emit, local_park;
+  uint32_t emit_base, park_base;
+  uint32_t thr_bin, thr_above, thr_count;
 };
 
 // Optional phase timeline of CTA 0 (row 0), compiled in with -DULC_TOPK_TRACE (development only):
@@ -74,17 +114,6 @@ __device__ long long topk_trace[16];
 #else
 #define TOPK_T(ev) do {} while (0)
 #endif
-
-// Cluster launch only: what a CTA selects is staged in its own shared memory first, so that it
-// claims its output and candidate ranges from CTA 0 with ONE remote atomic each (a remote atomic
-// per warp and element costs a cluster round trip every time).
-struct TopkStage {
-  uint32_t emit_key[2048];
-  int32_t emit_pos[2048];
-  uint32_t park_key[kTopkCand];
-  int32_t park_pos[kTopkCand];
-  uint32_t n_emit, n_park, emit_base, park_base;
-};
 
 // ---- distributed shared memory (cluster launch only) ------------------------------------------
 __device__ __forceinline__ uint32_t cluster_cta_rank() {
@@ -120,11 +149,12 @@ __device__ __forceinline__ void cluster_barrier() {
   asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
 }
 
-// Find digit d (scanning from the top bin down) where the running count first
-// reaches `need`; thr_above = number of elements in bins above d, thr_count =
-// elements in d.  `hist` is an array of NB counts in this CTA's shared memory.
+// Find bin d >= floor_bin (scanning from the top bin down) where the running count first reaches
+// `need`; thr_above = number of elements in bins above d, thr_count = elements in d.  Bins below
+// `floor_bin` are ignored; returns false when the bins from floor_bin up hold fewer than `need`.
 template <int NB>
-__device__ __forceinline__ void find_threshold(TopkShared& s, const uint32_t* hist, uint32_t need) {
+__device__ __forceinline__ bool find_threshold(TopkShared& s, const uint32_t* hist, uint32_t need,
+                                               uint32_t floor_bin = 0) {
   constexpr int PER = (NB + kTopkThreads - 1) / kTopkThreads;
   const int t = threadIdx.x;
   uint32_t local[PER];
@@ -132,9 +162,10 @@ __device__ __forceinline__ void find_threshold(TopkShared& s, const uint32_t* hi
 #pragma unroll
   for (int j = 0; j < PER; ++j) {
     const int rev = t * PER + j;   // position counted from the top
-    local[j] = rev < NB ? hist[NB - 1 - rev] : 0;
+    local[j] = (rev < NB && static_cast<uint32_t>(NB - 1 - rev) >= floor_bin) ? hist[NB - 1 - rev] : 0;
     sum += local[j];
   }
+  if (t == 0) s.thr_bin = 0xffffffffu;
   // exclusive block scan of `sum`
   uint32_t incl = sum;
 #pragma unroll
@@ -145,7 +176,7 @@ __device__ __forceinline__ void find_threshold(TopkShared& s, const uint32_t* hi
   if ((t & 31) == 31) s.warp_sums[t >> 5] = incl;
   __syncthreads();
   if (t < 32) {
-    uint32_t w = s.warp_sums[t];
+    uint32_t w = t < kTopkWarps ? s.warp_sums[t] : 0u;
 #pragma unroll
     for (int o = 1; o < 32; o <<= 1) {
       const uint32_t v = __shfl_up_sync(0xffffffffu, w, o);
@@ -166,19 +197,7 @@ __device__ __forceinline__ void find_threshold(TopkShared& s, const uint32_t* hi
     before += local[j];
   }
   __syncthreads();
-}
-
-// Cluster launch: add this CTA's non-empty histogram bins into `sum` of every CTA of the cluster
-// (its own included).  Most bins are empty, so this moves far less than reading CS histograms.
-// The adds need no result; the cluster barrier that follows makes them visible.
-template <int CS>
-__device__ __forceinline__ void push_histogram(const uint32_t* hist, uint32_t* sum) {
-  for (int b = threadIdx.x; b < kTopkBins; b += kTopkThreads) {
-    const uint32_t c = hist[b];
-    if (c == 0) continue;
-#pragma unroll
-    for (int r = 0; r < CS; ++r) dsm_add(dsm_addr(&sum[b], r), c);
-  }
+  return s.thr_bin != 0xffffffffu;
 }
 
 // How an emitted position becomes the output value.
@@ -225,144 +244,46 @@ __device__ __forceinline__ void write_out(int32_t* out_idx, float* out_val, int 
   }
 }
 
-// One CTA per row, two passes over the row with one shared-memory atomic per element: the shape
-// for many rows (every SM has a row of its own, so what counts is the work per row, and the
-// warp-aggregation and staging of the cluster kernel below only add instructions).
-__device__ __forceinline__ void emit_one(int32_t* out_idx, float* out_val, TopkShared& s, int k, int32_t pos,
-                                         uint32_t key, const TopkXform& x) {
-  write_out(out_idx, out_val, k, atomicAdd(&s.out_count, 1u), pos, key, x);
+__device__ __forceinline__ uint32_t warp_inclusive_scan(uint32_t v) {
+  const uint32_t lane = threadIdx.x & 31;
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    const uint32_t u = __shfl_up_sync(0xffffffffu, v, o);
+    if (lane >= static_cast<uint32_t>(o)) v += u;
+  }
+  return v;
 }
 
-__global__ void __launch_bounds__(kTopkThreads, 1)
-topk_row_kernel(const float* __restrict__ scores, long long row_stride, const int32_t* __restrict__ lengths,
-            int max_len, int k, const int32_t* __restrict__ in_idx, long long in_idx_stride,
-            const int32_t* __restrict__ xform, long long xform_stride, const int32_t* __restrict__ pages,
-            long long pages_stride, int rows_per_request, int ranks, int rank, int drop_neg_inf,
-            int32_t* __restrict__ out_idx, float* __restrict__ out_val, int32_t* __restrict__ out_count) {
-  extern __shared__ uint8_t topk_smem_raw[];
-  TopkShared& s = *reinterpret_cast<TopkShared*>(topk_smem_raw);
-  const int row = blockIdx.x;
-  const int t = threadIdx.x;
-  const float* x = scores + static_cast<size_t>(row) * row_stride;
-  TopkXform xf;
-  xf.in_idx = in_idx ? in_idx + static_cast<size_t>(row) * in_idx_stride : nullptr;
-  xf.table = xform ? xform + static_cast<size_t>(row) * xform_stride : nullptr;
-  xf.pages = pages ? pages + static_cast<size_t>(row / rows_per_request) * pages_stride : nullptr;
-  xf.ranks = ranks; xf.rank = rank; xf.drop_neg_inf = drop_neg_inf;
-  int32_t* oi = out_idx + static_cast<size_t>(row) * k;
-  float* ov = out_val ? out_val + static_cast<size_t>(row) * k : nullptr;
-  int n = lengths ? min(max(lengths[row], 0), max_len) : max_len;
+struct TopkArgs {
+  const float* scores; long long row_stride;
+  const int32_t* lengths; int max_len, k;
+  const int32_t* in_idx; long long in_idx_stride;
+  const int32_t* xform; long long xform_stride;
+  const int32_t* pages; long long pages_stride;
+  int rows_per_request, ranks, rank, drop_neg_inf;
+  int32_t* out_idx; float* out_val; int32_t* out_count;
+};
 
-  if (n <= k) {
-    for (int i = t; i < k; i += kTopkThreads) {
-      oi[i] = i < n ? xform_value(xf, i, x[i]) : -1;
-      if (ov) ov[i] = i < n ? x[i] : -INFINITY;
-    }
-    if (t == 0 && out_count) out_count[row] = n;
-    return;
-  }
-
-  for (int i = t; i < kTopkBins; i += kTopkThreads) s.hist[i] = 0;
-  if (t == 0) { s.out_count = 0; s.cand_count = 0; }
-  __syncthreads();
-  for (int i = t; i < n; i += kTopkThreads) atomicAdd(&s.hist[order_key(x[i]) >> 21], 1u);
-  __syncthreads();
-  find_threshold<kTopkBins>(s, s.hist, static_cast<uint32_t>(k));
-  const uint32_t b1 = s.thr_bin;
-  uint32_t need = static_cast<uint32_t>(k) - s.thr_above;
-  const uint32_t in_bin = s.hist[b1];
-  __syncthreads();
-
-  // pass 2: emit the bins above, park the threshold bin
-  for (int i = t; i < n; i += kTopkThreads) {
-    const uint32_t key = order_key(x[i]);
-    const uint32_t bin = key >> 21;
-    if (bin > b1) {
-      emit_one(oi, ov, s, k, i, key, xf);
-    } else if (bin == b1) {
-      const uint32_t c = atomicAdd(&s.cand_count, 1u);
-      if (c < kTopkCand) { s.cand_key[c] = key; s.cand_pos[c] = i; }
-    }
-  }
-  __syncthreads();
-  const bool in_smem = in_bin <= kTopkCand;
-  const int cn = in_smem ? static_cast<int>(in_bin) : n;
-
-  // Refinement over the composite (key, 0xffffffff - position), 11 bits a level.
-  // Level shifts are in the 64-bit composite; the top 11 bits are already fixed.
-  uint64_t prefix = static_cast<uint64_t>(b1) << 53;
-  uint64_t mask = 0x7ffull << 53;
-  bool done = (in_bin == need);
-  if (done) {   // the whole threshold bin is selected
-    for (int j = t; j < cn; j += kTopkThreads) {
-      uint32_t key; int32_t pos;
-      if (in_smem) { key = s.cand_key[j]; pos = s.cand_pos[j]; }
-      else { key = order_key(x[j]); pos = j; if ((key >> 21) != b1) continue; }
-      emit_one(oi, ov, s, k, pos, key, xf);
-    }
-  }
-  for (int shift = 42; !done; shift -= 11) {
-    const int sh = shift < 0 ? 0 : shift;
-    const uint32_t nb_mask = shift < 0 ? 0x1ffu : 0x7ffu;   // last level has 9 bits
-    for (int i = t; i < kTopkBins; i += kTopkThreads) s.hist[i] = 0;
-    __syncthreads();
-    for (int j = t; j < cn; j += kTopkThreads) {
-      uint32_t key; int32_t pos;
-      if (in_smem) { key = s.cand_key[j]; pos = s.cand_pos[j]; }
-      else { key = order_key(x[j]); pos = j; }
-      const uint64_t comp = (static_cast<uint64_t>(key) << 32) | (0xffffffffu - static_cast<uint32_t>(pos));
-      if ((comp & mask) == prefix) atomicAdd(&s.hist[(comp >> sh) & nb_mask], 1u);
-    }
-    __syncthreads();
-    find_threshold<kTopkBins>(s, s.hist, need);
-    const uint32_t d = s.thr_bin;
-    const uint32_t above = s.thr_above;
-    const uint32_t at_d = s.hist[d];
-    const bool last = (at_d == need - above) || shift < 0;
-    __syncthreads();
-    for (int j = t; j < cn; j += kTopkThreads) {
-      uint32_t key; int32_t pos;
-      if (in_smem) { key = s.cand_key[j]; pos = s.cand_pos[j]; }
-      else { key = order_key(x[j]); pos = j; }
-      const uint64_t comp = (static_cast<uint64_t>(key) << 32) | (0xffffffffu - static_cast<uint32_t>(pos));
-      if ((comp & mask) != prefix) continue;
-      const uint32_t dig = (comp >> sh) & nb_mask;
-      if (dig > d || (last && dig == d)) emit_one(oi, ov, s, k, pos, key, xf);
-    }
-    prefix |= static_cast<uint64_t>(d) << sh;
-    mask |= static_cast<uint64_t>(nb_mask) << sh;
-    need -= above;
-    done = last;
-    __syncthreads();
-  }
-  __syncthreads();
-  if (t == 0 && out_count) out_count[row] = min(static_cast<uint32_t>(k), s.out_count);
-}
-
-
-// CS = 1: one CTA per row.  CS > 1: launched with clusters of CS CTAs, one cluster per row.
+// CS CTAs per row (a cluster when CS > 1); `cap` blocks of keys fit the dynamic shared memory.
 template <int CS>
-__global__ void __launch_bounds__(kTopkThreads, 1)
-topk_kernel(const float* __restrict__ scores, long long row_stride, const int32_t* __restrict__ lengths,
-            int max_len, int k, const int32_t* __restrict__ in_idx, long long in_idx_stride,
-            const int32_t* __restrict__ xform, long long xform_stride, const int32_t* __restrict__ pages,
-            long long pages_stride, int rows_per_request, int ranks, int rank, int drop_neg_inf,
-            int32_t* __restrict__ out_idx, float* __restrict__ out_val, int32_t* __restrict__ out_count) {
-  extern __shared__ uint8_t topk_smem_raw[];
-  TopkShared& s = *reinterpret_cast<TopkShared*>(topk_smem_raw);
+__global__ void __launch_bounds__(kTopkThreads, 2)
+topk_select_kernel(const TopkArgs a, const int cap) {
+  __shared__ TopkShared s;
+  extern __shared__ uint32_t topk_keys[];          // [cap][512] keys of this CTA's blocks
   const int row = blockIdx.x / CS;
   const uint32_t crank = CS > 1 ? cluster_cta_rank() : 0u;
   const int t = threadIdx.x;
   const uint32_t lane = t & 31;
-  const float* x = scores + static_cast<size_t>(row) * row_stride;
+  const float* x = a.scores + static_cast<size_t>(row) * a.row_stride;
   TopkXform xf;
-  xf.in_idx = in_idx ? in_idx + static_cast<size_t>(row) * in_idx_stride : nullptr;
-  xf.table = xform ? xform + static_cast<size_t>(row) * xform_stride : nullptr;
-  xf.pages = pages ? pages + static_cast<size_t>(row / rows_per_request) * pages_stride : nullptr;
-  xf.ranks = ranks; xf.rank = rank; xf.drop_neg_inf = drop_neg_inf;
-  int32_t* oi = out_idx + static_cast<size_t>(row) * k;
-  float* ov = out_val ? out_val + static_cast<size_t>(row) * k : nullptr;
-  const int n = lengths ? min(max(lengths[row], 0), max_len) : max_len;
+  xf.in_idx = a.in_idx ? a.in_idx + static_cast<size_t>(row) * a.in_idx_stride : nullptr;
+  xf.table = a.xform ? a.xform + static_cast<size_t>(row) * a.xform_stride : nullptr;
+  xf.pages = a.pages ? a.pages + static_cast<size_t>(row / a.rows_per_request) * a.pages_stride : nullptr;
+  xf.ranks = a.ranks; xf.rank = a.rank; xf.drop_neg_inf = a.drop_neg_inf;
+  const int k = a.k;
+  int32_t* oi = a.out_idx + static_cast<size_t>(row) * k;
+  float* ov = a.out_val ? a.out_val + static_cast<size_t>(row) * k : nullptr;
+  const int n = a.lengths ? min(max(a.lengths[row], 0), a.max_len) : a.max_len;
 
   if (n <= k) {   // the same decision in every CTA of the cluster, before any cluster barrier
     if (crank == 0) {
@@ -370,234 +291,369 @@ topk_kernel(const float* __restrict__ scores, long long row_stride, const int32_
         oi[i] = i < n ? xform_value(xf, i, x[i]) : -1;
         if (ov) ov[i] = i < n ? x[i] : -INFINITY;
       }
-      if (t == 0 && out_count) out_count[row] = n;
+      if (t == 0 && a.out_count) a.out_count[row] = n;
     }
     return;
   }
 
   TOPK_T(0);
-  for (int i = t; i < kTopkBins; i += kTopkThreads) {
-    s.hist[i] = 0;
-    if constexpr (CS > 1) { s.sum1[i] = 0; s.sum2[i] = 0; }
-  }
-  if (t == 0) { s.out_count = 0; s.cand_count = 0; }
-  __syncthreads();
-  // The other CTAs add into sum1 / sum2 of this one: tell them they are cleared.  The wait for
-  // their arrival comes after the first pass, which touches local memory only.
-  if constexpr (CS > 1) cluster_arrive();
-  TOPK_T(1);
-
-  // Blocks of 1024 consecutive elements are dealt to the CTAs of the cluster in turn.  A CTA
-  // with at most kTopkRegs blocks (rows up to CS * kTopkRegs * 1024 elements) loads each element
-  // once and keeps its key in a register for all passes; longer rows are re-read chunk by chunk.
   // Key 0 marks "no element": no float maps to it (order_key sends every NaN to the key of -inf),
-  // and its bin, 0, lies below every valid key, so it can never reach the threshold.
+  // and it lies below every cut-off used here.
   const uint32_t un = static_cast<uint32_t>(n);
   const uint32_t nblk = (un + kTopkThreads - 1) / kTopkThreads;
   const uint32_t my_blocks = nblk > crank ? (nblk - crank + CS - 1) / CS : 0;
-  const uint32_t chunks = (my_blocks + kTopkRegs - 1) / kTopkRegs;
+  const uint32_t E = static_cast<uint32_t>(cap);
+  const uint32_t chunks = (my_blocks + E - 1) / E;
   const bool cached = chunks <= 1;
-  uint32_t keys[kTopkRegs];
-  auto element = [&](uint32_t chunk, int j) -> uint32_t {       // row position of keys[j] in `chunk`
-    return (crank + (chunk * kTopkRegs + j) * CS) * kTopkThreads + t;
+  uint32_t* keys = topk_keys + t;                                // keys[j * 512]: key j of this thread
+  constexpr uint32_t KS = kTopkThreads;
+  auto element = [&](uint32_t chunk, uint32_t j) -> uint32_t {  // row position of key j of `chunk`
+    return (crank + (chunk * E + j) * CS) * kTopkThreads + t;
   };
+  auto chunk_len = [&](uint32_t chunk) -> uint32_t { return min(E, my_blocks - chunk * E); };
   auto load_chunk = [&](uint32_t chunk) {
-#pragma unroll
-    for (int j = 0; j < kTopkRegs; ++j) {
+    const uint32_t nj = chunk_len(chunk);
+#pragma unroll 4
+    for (uint32_t j = 0; j < nj; ++j) {
       const uint32_t i = element(chunk, j);
-      keys[j] = (chunk * kTopkRegs + j < my_blocks && i < un) ? order_key(x[i]) : 0u;
+      keys[j * KS] = i < un ? order_key(__ldg(x + i)) : 0u;
     }
   };
+  load_chunk(0);
 
-  // pass 1: histogram of key bits 31..21 over this CTA's blocks
-  for (uint32_t chunk = 0; chunk < chunks; ++chunk) {
-    load_chunk(chunk);
-#pragma unroll
-    for (int j = 0; j < kTopkRegs; ++j) {
-      const uint32_t bin = keys[j] >> 21;
-      const uint32_t peers = __match_any_sync(0xffffffffu, bin);
-      if (keys[j] != 0u && lane == static_cast<uint32_t>(__ffs(peers) - 1)) atomicAdd(&s.hist[bin], static_cast<uint32_t>(__popc(peers)));
-    }
+  for (int i = t; i < kTopkBins; i += kTopkThreads) {
+    s.hist[i] = 0;
+    if constexpr (CS > 1) { s.sum[i] = 0; s.sum2[i] = 0; }
   }
+  if (t < kTopkFilters) s.filt_count[t] = 0;
+  if (t == 0) { s.out_count = 0; s.cand_count = 0; s.local_emit = 0; s.local_park = 0; }
+  // ---- step 1: filter ---------------------------------------------------------------------
+  // 32 keys from 32 threads, spread over this CTA's blocks
+  if ((t & 15) == 0) s.sample[t >> 4] = my_blocks ? keys[((t >> 4) % chunk_len(0)) * KS] : 0u;
   __syncthreads();
+  // The other CTAs add into `sum` of this one: tell them it is cleared.  The wait for their
+  // arrival comes after the local passes.
+  if constexpr (CS > 1) cluster_arrive();
+  TOPK_T(1);
+  const uint32_t target = (3u * static_cast<uint32_t>(k) / 2u + CS - 1) / CS + 32u;   // survivors this CTA wants
+  const uint32_t n_local = min(my_blocks * kTopkThreads, un);
+  const bool filtering = 2u * target < n_local;
+  uint32_t filter_key = 1u, filter_bin = 0u;                     // pass everything
+  if (filtering) {
+    if (t < 32) {
+      uint32_t v = s.sample[lane];
+#pragma unroll
+      for (int kk = 2; kk <= 32; kk <<= 1)
+#pragma unroll
+        for (int j = kk >> 1; j > 0; j >>= 1) {                  // bitonic sort, descending
+          const uint32_t o = __shfl_xor_sync(0xffffffffu, v, j);
+          const bool keep_max = ((lane & j) == 0) == ((lane & kk) == 0);
+          v = keep_max ? max(v, o) : min(v, o);
+        }
+      // eight ranks around the one whose cut-off is expected to leave `target` elements
+      const float expect = 33.f * static_cast<float>(target) / static_cast<float>(n_local);
+      const int c = lane < kTopkFilters ? lane : 0;
+      const int r = min(32, max(1, static_cast<int>(ceilf(expect * kTopkRankSpread[c]))));
+      const uint32_t cut = __shfl_sync(0xffffffffu, v, r - 1);
+      if (lane < kTopkFilters) s.filt_key[lane] = cut == 0u ? 1u : bin_lo_key(window_bin(cut));   // bin aligned
+    }
+    __syncthreads();
+    uint32_t fk[kTopkFilters], cnt[kTopkFilters];
+#pragma unroll
+    for (int c = 0; c < kTopkFilters; ++c) { fk[c] = s.filt_key[c]; cnt[c] = 0; }
+    for (uint32_t chunk = 0; chunk < chunks; ++chunk) {
+      if (chunk > 0) { __syncthreads(); load_chunk(chunk); }
+      const uint32_t nj = chunk_len(chunk);
+#pragma unroll 1
+      for (uint32_t j = 0; j < nj; ++j) {
+        const uint32_t key = keys[j * KS];
+#pragma unroll
+        for (int c = 0; c < kTopkFilters; ++c) cnt[c] += key >= fk[c] ? 1u : 0u;
+      }
+    }
+#pragma unroll
+    for (int c = 0; c < kTopkFilters; ++c) {
+      const uint32_t w = __reduce_add_sync(0xffffffffu, cnt[c]);
+      if (lane == 0 && w) atomicAdd(&s.filt_count[c], w);
+    }
+    __syncthreads();
+#pragma unroll
+    for (int c = kTopkFilters - 1; c >= 0; --c)                   // the highest cut-off that leaves enough
+      if (s.filt_count[c] >= target) { filter_key = fk[c]; }
+    filter_bin = filter_key == 1u ? 0u : window_bin(filter_key);
+  }
   TOPK_T(2);
-  const uint32_t* level_hist = s.hist;
-  if constexpr (CS > 1) {
-    cluster_wait();                      // every CTA has cleared its sums
-    push_histogram<CS>(s.hist, s.sum1);
-    cluster_barrier();                   // ... and has received everybody's counts
-    level_hist = s.sum1;
+
+  // ---- step 2: histogram of the survivors, merged over the cluster ---------------------------
+  uint32_t b1 = 0, need = 0, in_bin = 0;
+  bool first_try = true;
+  while (true) {
+    for (uint32_t chunk = 0; chunk < chunks; ++chunk) {
+      if (!cached) load_chunk(chunk);
+      const uint32_t nj = chunk_len(chunk);
+#pragma unroll 1
+      for (uint32_t j = 0; j < nj; ++j) {
+        const uint32_t key = keys[j * KS];
+        if (key >= filter_key) atomicAdd(&s.hist[window_bin(key)], 1u);
+      }
+    }
+    __syncthreads();
+    const uint32_t* row_hist = s.hist;
+    uint32_t floor_bin = filter_bin;
+    if constexpr (CS > 1) {
+      if (first_try) cluster_wait();       // every CTA has cleared its sums
+      for (int b = t; b < kTopkBins; b += kTopkThreads) {
+        const uint32_t c = s.hist[b];
+        if (c == 0) continue;              // most bins are empty
+#pragma unroll
+        for (int r = 0; r < CS; ++r) dsm_add(dsm_addr(&s.sum[b], r), c);
+      }
+      if (t < CS) dsm_store(dsm_addr(&s.filt_bin[crank], t), filter_bin);
+      cluster_barrier();                   // ... and has received everybody's counts
+      row_hist = s.sum;
+#pragma unroll
+      for (int r = 0; r < CS; ++r) floor_bin = max(floor_bin, s.filt_bin[r]);
+    }
+    // the row histogram is exact from the cluster's highest filter bin upwards
+    const bool found = find_threshold<kTopkBins>(s, row_hist, static_cast<uint32_t>(k), floor_bin);
+    if (found) break;
+    // The filter cut too deep (a sample that misjudged the row): once more with every element.
+    // All CTAs of the cluster read the same histogram, so all of them come here together.
+    first_try = false;
+    filter_key = 1u;
+    filter_bin = 0u;
+    if constexpr (CS > 1) cluster_barrier();          // nobody still reads the sums
+    for (int i = t; i < kTopkBins; i += kTopkThreads) {
+      s.hist[i] = 0;
+      if constexpr (CS > 1) s.sum[i] = 0;
+    }
+    __syncthreads();
+    if constexpr (CS > 1) cluster_barrier();          // every sum is cleared before anybody adds
   }
   TOPK_T(3);
-  find_threshold<kTopkBins>(s, level_hist, static_cast<uint32_t>(k));
-  TOPK_T(4);
-  const uint32_t b1 = s.thr_bin;
-  uint32_t need = static_cast<uint32_t>(k) - s.thr_above;
-  uint32_t in_bin = s.thr_count;
-  __syncthreads();
-
-  // Scores of one request sit within an octave or two, so the threshold bin of the first level
-  // often holds thousands of elements.  A second histogram level (key bits 20..10) over that bin
-  // costs one more pass (over registers, or over the row in L2) and leaves a handful of
-  // candidates to refine.
-  uint32_t sel_shift = 21;          // elements are classified by key >> sel_shift against sel_prefix
-  uint32_t sel_prefix = b1;
-  const bool two_level = in_bin > kTopkSmallBin && in_bin != need;
-  if (two_level) {
-    for (int i = t; i < kTopkBins; i += kTopkThreads) s.hist[i] = 0;     // only this CTA reads its hist
+  b1 = s.thr_bin;
+  need = static_cast<uint32_t>(k) - s.thr_above;      // how many of the threshold bin are selected
+  in_bin = s.thr_count;
+  uint32_t key_cand = bin_lo_key(b1);                                      // candidates: key_cand <= key < key_above
+  uint64_t key_above = b1 < 2047u ? bin_lo_key(b1 + 1u) : kNoKey;          // selected outright
+  if (in_bin > static_cast<uint32_t>(kTopkCand) && in_bin != need) {
+    // A crowded threshold bin (scores packed into a fraction of an octave): a second level of
+    // 2048 equal key ranges inside it.
+    const uint32_t lo = key_cand;
+    const uint32_t width = static_cast<uint32_t>(key_above - lo);          // modulo 2^32 for the top bin; never 0
+    const int sh = width - 1u < 2048u ? 0 : (32 - __clz(width - 1u)) - 11;
+    for (int i = t; i < kTopkBins; i += kTopkThreads) s.hist[i] = 0;
     __syncthreads();
     for (uint32_t chunk = 0; chunk < chunks; ++chunk) {
       if (!cached) load_chunk(chunk);
+      const uint32_t nj = chunk_len(chunk);
+#pragma unroll 1
+      for (uint32_t j = 0; j < nj; ++j) {
+        const uint32_t key = keys[j * KS];
+        if (key >= lo && static_cast<uint64_t>(key) < key_above) atomicAdd(&s.hist[(key - lo) >> sh], 1u);
+      }
+    }
+    __syncthreads();
+    const uint32_t* sub_hist = s.hist;
+    if constexpr (CS > 1) {
+      for (int b = t; b < kTopkBins; b += kTopkThreads) {
+        const uint32_t c = s.hist[b];
+        if (c == 0) continue;
 #pragma unroll
-      for (int j = 0; j < kTopkRegs; ++j) {
-        const bool in1 = (keys[j] >> 21) == b1;
-        const uint32_t bin = in1 ? ((keys[j] >> 10) & 0x7ffu) : 0xffffffffu;
-        const uint32_t peers = __match_any_sync(0xffffffffu, bin);
-        if (in1 && lane == static_cast<uint32_t>(__ffs(peers) - 1)) atomicAdd(&s.hist[bin], static_cast<uint32_t>(__popc(peers)));
+        for (int r = 0; r < CS; ++r) dsm_add(dsm_addr(&s.sum2[b], r), c);
+      }
+      cluster_barrier();
+      sub_hist = s.sum2;
+    }
+    find_threshold<kTopkBins>(s, sub_hist, need);     // the bin holds at least `need` elements
+    const uint32_t b2 = s.thr_bin;
+    need -= s.thr_above;
+    in_bin = s.thr_count;
+    key_cand = lo + (b2 << sh);
+    if (b2 < 2047u) key_above = static_cast<uint64_t>(lo) + (static_cast<uint64_t>(b2 + 1u) << sh);
+  }
+  const bool parked = in_bin <= static_cast<uint32_t>(kTopkCand);
+  TOPK_T(4);
+
+  // ---- step 3: emit ------------------------------------------------------------------------------
+  {
+    uint32_t na = 0, nc = 0;
+    for (uint32_t chunk = 0; chunk < chunks; ++chunk) {
+      if (!cached) load_chunk(chunk);
+      const uint32_t nj = chunk_len(chunk);
+#pragma unroll 1
+      for (uint32_t j = 0; j < nj; ++j) {
+        const uint32_t key = keys[j * KS];
+        const bool above = static_cast<uint64_t>(key) >= key_above;
+        na += above ? 1u : 0u;
+        nc += (!above && key >= key_cand) ? 1u : 0u;
+      }
+    }
+    if (!parked) nc = 0;
+    const uint32_t ia = warp_inclusive_scan(na), ic = warp_inclusive_scan(nc);
+    uint32_t wa = 0, wc = 0;
+    if (lane == 31) {
+      wa = ia ? atomicAdd(&s.local_emit, ia) : 0u;
+      wc = ic ? atomicAdd(&s.local_park, ic) : 0u;
+    }
+    wa = __shfl_sync(0xffffffffu, wa, 31);
+    wc = __shfl_sync(0xffffffffu, wc, 31);
+    __syncthreads();
+    if (t == 0) {
+      const uint32_t above = s.local_emit, park = s.local_park;
+      if constexpr (CS > 1) {
+        s.emit_base = above ? dsm_atomic_add(dsm_addr(&s.out_count, 0), above) : 0u;
+        s.park_base = park ? dsm_atomic_add(dsm_addr(&s.cand_count, 0), park) : 0u;
+      } else {
+        s.emit_base = 0; s.park_base = 0;
+        s.out_count = above; s.cand_count = park;
       }
     }
     __syncthreads();
     TOPK_T(5);
-    if constexpr (CS > 1) {
-      push_histogram<CS>(s.hist, s.sum2);
-      cluster_barrier();
-      level_hist = s.sum2;
-    }
-    TOPK_T(6);
-    find_threshold<kTopkBins>(s, level_hist, need);
-    TOPK_T(7);
-    const uint32_t b2 = s.thr_bin;
-    need -= s.thr_above;
-    in_bin = s.thr_count;
-    __syncthreads();
-    sel_shift = 10;
-    sel_prefix = (b1 << 11) | b2;
-  }
-
-  // emit pass: everything above the threshold prefix goes out, the threshold bin is parked
-  // (in CTA 0's shared memory)
-  TopkStage* stage = nullptr;
-  if constexpr (CS > 1) {
-    stage = reinterpret_cast<TopkStage*>(topk_smem_raw + sizeof(TopkShared));
-    if (t == 0) { stage->n_emit = 0; stage->n_park = 0; }
-    __syncthreads();
-  }
-  for (uint32_t chunk = 0; chunk < chunks; ++chunk) {
-    if (!cached) load_chunk(chunk);
-#pragma unroll
-    for (int j = 0; j < kTopkRegs; ++j) {
-      const uint32_t key = keys[j];
-      const uint32_t i = element(chunk, j);
-      const uint32_t pre = key >> sel_shift;          // key 0 ("no element") is below every prefix
-      if constexpr (CS > 1) {
-        const uint32_t at = claim_slots(&stage->n_emit, pre > sel_prefix);
-        if (at < 2048u) { stage->emit_key[at] = key; stage->emit_pos[at] = static_cast<int32_t>(i); }
-        const uint32_t c = claim_slots(&stage->n_park, pre == sel_prefix);
-        if (c < static_cast<uint32_t>(kTopkCand)) { stage->park_key[c] = key; stage->park_pos[c] = static_cast<int32_t>(i); }
-      } else {
-        const uint32_t at = claim_slots(&s.out_count, pre > sel_prefix);
-        if (at != 0xffffffffu) write_out(oi, ov, k, at, static_cast<int32_t>(i), key, xf);
-        const uint32_t c = claim_slots(&s.cand_count, pre == sel_prefix);
-        if (c < static_cast<uint32_t>(kTopkCand)) {
-          s.cand_key[c] = key;
-          s.cand_pos[c] = static_cast<int32_t>(i);
+    uint32_t pa = s.emit_base + wa + ia - na, pc = s.park_base + wc + ic - nc;
+    const uint32_t m_key = CS > 1 ? dsm_addr(&s.cand_key[0], 0) : 0u;
+    const uint32_t m_pos = CS > 1 ? dsm_addr(&s.cand_pos[0], 0) : 0u;
+    for (uint32_t chunk = 0; chunk < chunks; ++chunk) {
+      if (!cached) load_chunk(chunk);
+      const uint32_t nj = chunk_len(chunk);
+#pragma unroll 1
+      for (uint32_t j = 0; j < nj; ++j) {
+        const uint32_t key = keys[j * KS];
+        const uint32_t i = element(chunk, j);
+        if (static_cast<uint64_t>(key) >= key_above) {
+          write_out(oi, ov, k, pa++, static_cast<int32_t>(i), key, xf);
+        } else if (parked && key >= key_cand) {
+          if (pc < static_cast<uint32_t>(kTopkCand)) {
+            if constexpr (CS > 1) {
+              dsm_store(m_key + pc * 4u, key);
+              dsm_store(m_pos + pc * 4u, i);
+            } else {
+              s.cand_key[pc] = key;
+              s.cand_pos[pc] = static_cast<int32_t>(i);
+            }
+          }
+          ++pc;
         }
       }
     }
   }
-  TOPK_T(8);
+  TOPK_T(6);
   if constexpr (CS > 1) {
-    __syncthreads();
-    if (t == 0) {
-      stage->emit_base = dsm_atomic_add(dsm_addr(&s.out_count, 0), stage->n_emit);
-      stage->park_base = dsm_atomic_add(dsm_addr(&s.cand_count, 0), stage->n_park);
-    }
-    __syncthreads();
-    // fewer than k elements lie above the threshold in the whole row, so the staged ones all fit
-    const uint32_t ne = min(stage->n_emit, 2048u), eb = stage->emit_base;
-    for (uint32_t i = t; i < ne; i += kTopkThreads) write_out(oi, ov, k, eb + i, stage->emit_pos[i], stage->emit_key[i], xf);
-    const uint32_t np = min(stage->n_park, static_cast<uint32_t>(kTopkCand)), pb = stage->park_base;
-    const uint32_t m_key = dsm_addr(&s.cand_key[0], 0), m_pos = dsm_addr(&s.cand_pos[0], 0);
-    for (uint32_t i = t; i < np; i += kTopkThreads) {
-      const uint32_t dst = pb + i;
-      if (dst < static_cast<uint32_t>(kTopkCand)) {
-        dsm_store(m_key + dst * 4u, stage->park_key[i]);
-        dsm_store(m_pos + dst * 4u, static_cast<uint32_t>(stage->park_pos[i]));
-      }
-    }
-  }
-  TOPK_T(9);
-  if constexpr (CS > 1) {
-    // After this barrier nobody reads or writes another CTA's shared memory: CTA 0 refines alone.
+    // After this barrier nobody reads or writes another CTA's shared memory: CTA 0 finishes alone.
     cluster_barrier();
-    TOPK_T(10);
     if (crank != 0) return;
   } else {
     __syncthreads();
   }
-  const bool in_smem = in_bin <= kTopkCand;
-  const int cn = in_smem ? static_cast<int>(in_bin) : n;
+  TOPK_T(7);
 
-  // Refinement over the composite (key, 0xffffffff - position), 11 bits a level.
-  // Level shifts are in the 64-bit composite; the top 11 (or 22) bits are already fixed.
-  uint64_t prefix = static_cast<uint64_t>(sel_prefix) << (32 + sel_shift);
-  uint64_t mask = (two_level ? 0x3fffffull : 0x7ffull) << (32 + sel_shift);
-  bool done = (in_bin == need);
-  if (done) {   // the whole threshold bin is selected
+  // ---- step 4: resolve the threshold bin (CTA 0) ---------------------------------------------------
+  const int cn = parked ? static_cast<int>(in_bin) : n;
+  auto in_range = [&](uint32_t key) { return key >= key_cand && static_cast<uint64_t>(key) < key_above; };
+  if (in_bin == need) {   // the whole threshold bin is selected
     for (int jb = 0; jb < cn; jb += kTopkThreads) {
       const int j = jb + t;
       uint32_t key = 0; int32_t pos = 0;
       bool take = j < cn;
       if (take) {
-        if (in_smem) { key = s.cand_key[j]; pos = s.cand_pos[j]; }
-        else { key = order_key(x[j]); pos = j; take = (key >> sel_shift) == sel_prefix; }
+        if (parked) { key = s.cand_key[j]; pos = s.cand_pos[j]; }
+        else { key = order_key(x[j]); pos = j; take = in_range(key); }
       }
       const uint32_t at = claim_slots(&s.out_count, take);
       if (at != 0xffffffffu) write_out(oi, ov, k, at, pos, key, xf);
     }
-  }
-  for (int shift = two_level ? 31 : 42; !done; shift -= 11) {
-    const int sh = shift < 0 ? 0 : shift;
-    const uint32_t nb_mask = shift < 0 ? 0x1ffu : 0x7ffu;   // last level has 9 bits
-    for (int i = t; i < kTopkBins; i += kTopkThreads) s.hist[i] = 0;
-    __syncthreads();
-    for (int j = t; j < cn; j += kTopkThreads) {
-      uint32_t key; int32_t pos;
-      if (in_smem) { key = s.cand_key[j]; pos = s.cand_pos[j]; }
-      else { key = order_key(x[j]); pos = j; }
-      const uint64_t comp = (static_cast<uint64_t>(key) << 32) | (0xffffffffu - static_cast<uint32_t>(pos));
-      if ((comp & mask) == prefix) atomicAdd(&s.hist[(comp >> sh) & nb_mask], 1u);
+  } else if (parked && cn <= kTopkRankMax) {
+    // Few candidates: a candidate is selected iff fewer than `need` candidates beat it, where
+    // "beats" compares the score and then prefers the lower position.  G threads share a candidate.
+    int P = 16;
+    while (P < cn) P <<= 1;
+    const int G = kTopkThreads / P;              // 1 .. 32 consecutive lanes per candidate
+    const int j = t / G, g = t % G;
+    uint32_t key = 0; int32_t pos = 0;
+    uint32_t rank = 0;
+    if (j < cn) {
+      key = s.cand_key[j]; pos = s.cand_pos[j];
+      for (int i = g; i < cn; i += G) {
+        const uint32_t ki = s.cand_key[i];
+        const int32_t pi = s.cand_pos[i];
+        rank += (ki > key || (ki == key && pi < pos)) ? 1u : 0u;
+      }
     }
-    __syncthreads();
-    find_threshold<kTopkBins>(s, s.hist, need);
-    const uint32_t d = s.thr_bin;
-    const uint32_t above = s.thr_above;
-    const uint32_t at_d = s.thr_count;
-    const bool last = (at_d == need - above) || shift < 0;
-    __syncthreads();
-    for (int jb = 0; jb < cn; jb += kTopkThreads) {
-      const int j = jb + t;
-      uint32_t key = 0; int32_t pos = 0;
-      bool take = false;
-      if (j < cn) {
-        if (in_smem) { key = s.cand_key[j]; pos = s.cand_pos[j]; }
-        else { key = order_key(x[j]); pos = j; }
+    for (int o = 1; o < G; o <<= 1) rank += __shfl_xor_sync(0xffffffffu, rank, o);
+    const bool take = j < cn && g == 0 && rank < need;
+    const uint32_t at = claim_slots(&s.out_count, take);
+    if (at != 0xffffffffu) write_out(oi, ov, k, at, pos, key, xf);
+  } else {
+    // Radix levels over the 64-bit composite (key, 0xffffffff - position), 11 bits a level,
+    // over the parked candidates or (a threshold range too crowded to park) over the row itself.
+    uint64_t prefix = 0, mask = 0;
+    bool done = false;
+    for (int shift = 53; !done; shift -= 11) {
+      const int sh = shift < 0 ? 0 : shift;
+      const uint32_t nb_mask = shift < 0 ? 0x1ffu : 0x7ffu;   // the last level has 9 bits
+      for (int i = t; i < kTopkBins; i += kTopkThreads) s.hist[i] = 0;
+      __syncthreads();
+      for (int j = t; j < cn; j += kTopkThreads) {
+        uint32_t key; int32_t pos;
+        if (parked) { key = s.cand_key[j]; pos = s.cand_pos[j]; }
+        else { key = order_key(x[j]); pos = j; if (!in_range(key)) continue; }
         const uint64_t comp = (static_cast<uint64_t>(key) << 32) | (0xffffffffu - static_cast<uint32_t>(pos));
-        const uint32_t dig = (comp >> sh) & nb_mask;
-        take = (comp & mask) == prefix && (dig > d || (last && dig == d));
+        if ((comp & mask) == prefix) atomicAdd(&s.hist[(comp >> sh) & nb_mask], 1u);
       }
-      const uint32_t at = claim_slots(&s.out_count, take);
-      if (at != 0xffffffffu) write_out(oi, ov, k, at, pos, key, xf);
+      __syncthreads();
+      find_threshold<kTopkBins>(s, s.hist, need);
+      const uint32_t d = s.thr_bin;
+      const uint32_t above = s.thr_above;
+      const uint32_t at_d = s.thr_count;
+      const bool last = (at_d == need - above) || shift < 0;
+      __syncthreads();
+      for (int jb = 0; jb < cn; jb += kTopkThreads) {
+        const int j = jb + t;
+        uint32_t key = 0; int32_t pos = 0;
+        bool take = false;
+        if (j < cn) {
+          if (parked) { key = s.cand_key[j]; pos = s.cand_pos[j]; take = true; }
+          else { key = order_key(x[j]); pos = j; take = in_range(key); }
+          const uint64_t comp = (static_cast<uint64_t>(key) << 32) | (0xffffffffu - static_cast<uint32_t>(pos));
+          const uint32_t dig = (comp >> sh) & nb_mask;
+          take = take && (comp & mask) == prefix && (dig > d || (last && dig == d));
+        }
+        const uint32_t at = claim_slots(&s.out_count, take);
+        if (at != 0xffffffffu) write_out(oi, ov, k, at, pos, key, xf);
+      }
+      prefix |= static_cast<uint64_t>(d) << sh;
+      mask |= static_cast<uint64_t>(nb_mask) << sh;
+      need -= above;
+      done = last;
+      __syncthreads();
     }
-    prefix |= static_cast<uint64_t>(d) << sh;
-    mask |= static_cast<uint64_t>(nb_mask) << sh;
-    need -= above;
-    done = last;
-    __syncthreads();
   }
   __syncthreads();
-  TOPK_T(11);
-  if (t == 0 && out_count) out_count[row] = min(static_cast<uint32_t>(k), s.out_count);
+  TOPK_T(8);
+  if (t == 0 && a.out_count) a.out_count[row] = min(static_cast<uint32_t>(k), s.out_count);
+}
+
+template <int CS>
+static int launch_topk(const TopkArgs& a, int rows, int cap, cudaStream_t stream) {
+  static PerDeviceOnce once;
+  const int key_bytes = cap * kTopkThreads * 4;
+  int rc = ensure_dynamic_smem(reinterpret_cast<const void*>(topk_select_kernel<CS>), 32 * kTopkThreads * 4, once);
+  if (rc != 0) return rc;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(static_cast<unsigned>(rows) * CS);
+  cfg.blockDim = dim3(kTopkThreads);
+  cfg.dynamicSmemBytes = key_bytes;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = CS;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = CS > 1 ? 1 : 0;
+  cudaError_t e = cudaLaunchKernelEx(&cfg, topk_select_kernel<CS>, a, cap);
+  return static_cast<int>(e != cudaSuccess ? e : cudaGetLastError());
 }
 
 }  // namespace ulc
@@ -628,41 +684,31 @@ int ulc_topk_ex(const float* scores, long long row_stride, const int32_t* length
   if (rows <= 0) return 0;
   if (k <= 0 || k > 2048 || max_len < 0) return -kErrUnsupported;
   if (rows_per_request < 1) rows_per_request = 1;
-  static bool configured = false;
-  if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(topk_row_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         static_cast<int>(sizeof(TopkShared)));
-    if (e == cudaSuccess)
-      e = cudaFuncSetAttribute(topk_kernel<kTopkCluster>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                               static_cast<int>(sizeof(TopkShared) + sizeof(TopkStage)));
-    if (e != cudaSuccess) return static_cast<int>(e);
-    configured = true;
-  }
-  // Few long rows: a cluster per row keeps more SMs busy.  mode: 0 = choose, 1 = one CTA per row, 2 = cluster.
+  TopkArgs a;
+  a.scores = scores; a.row_stride = row_stride; a.lengths = lengths; a.max_len = max_len; a.k = k;
+  a.in_idx = in_idx; a.in_idx_stride = in_idx_stride; a.xform = xform; a.xform_stride = xform_stride;
+  a.pages = pages; a.pages_stride = pages_stride; a.rows_per_request = rows_per_request;
+  a.ranks = ranks; a.rank = rank; a.drop_neg_inf = drop_neg_inf;
+  a.out_idx = out_idx; a.out_val = out_val; a.out_count = out_count;
+  // CTAs per row: enough that a row's keys stay in shared memory with two CTAs per SM (16 blocks
+  // each), then more while the launch still fits the machine in one wave.
+  // mode: 0 = choose, 1 = one CTA per row, 2 = a cluster of eight per row.
   const int mode = g_topk_mode;
-  const bool cluster = mode == 2 || (mode == 0 && rows * kTopkCluster <= 2 * 148 && max_len >= 4 * kTopkThreads * kTopkCluster);
-  if (cluster) {
-    cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3(static_cast<unsigned>(rows) * kTopkCluster);
-    cfg.blockDim = dim3(kTopkThreads);
-    cfg.dynamicSmemBytes = sizeof(TopkShared) + sizeof(TopkStage);
-    cfg.stream = stream;
-    cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeClusterDimension;
-    attr[0].val.clusterDim.x = kTopkCluster;
-    attr[0].val.clusterDim.y = 1;
-    attr[0].val.clusterDim.z = 1;
-    cfg.attrs = attr;
-    cfg.numAttrs = 1;
-    cudaError_t e = cudaLaunchKernelEx(&cfg, topk_kernel<kTopkCluster>, scores, row_stride, lengths, max_len, k,
-                                       in_idx, in_idx_stride, xform, xform_stride, pages, pages_stride,
-                                       rows_per_request, ranks, rank, drop_neg_inf, out_idx, out_val, out_count);
-    return static_cast<int>(e != cudaSuccess ? e : cudaGetLastError());
+  int cs = 1;
+  while (cs < kTopkMaxCluster && static_cast<long long>(cs) * kTopkThreads * 16 < max_len) cs *= 2;
+  while (cs < kTopkMaxCluster && static_cast<long long>(rows) * cs * 2 <= 2 * 148) cs *= 2;
+  if (max_len <= 2 * k) cs = 1;       // short candidate lists: one CTA, nothing to share
+  if (mode == 1) cs = 1;
+  if (mode == 2) cs = kTopkMaxCluster;
+  // blocks of keys a CTA holds in shared memory: its whole share of the row when that is at most 32
+  long long cap = (static_cast<long long>(max_len) + cs * kTopkThreads - 1) / (cs * kTopkThreads);
+  cap = cap < 1 ? 1 : (cap > 32 ? 32 : cap);
+  switch (cs) {
+    case 1: return launch_topk<1>(a, rows, static_cast<int>(cap), stream);
+    case 2: return launch_topk<2>(a, rows, static_cast<int>(cap), stream);
+    case 4: return launch_topk<4>(a, rows, static_cast<int>(cap), stream);
+    default: return launch_topk<8>(a, rows, static_cast<int>(cap), stream);
   }
-  topk_row_kernel<<<rows, kTopkThreads, sizeof(TopkShared), stream>>>(
-      scores, row_stride, lengths, max_len, k, in_idx, in_idx_stride, xform, xform_stride, pages, pages_stride,
-      rows_per_request, ranks, rank, drop_neg_inf, out_idx, out_val, out_count);
-  return static_cast<int>(cudaGetLastError());
 }
 
 #ifdef ULC_TOPK_TRACE
@@ -671,7 +717,7 @@ int ulc_topk_trace_read(long long* host) {
 }
 #endif
 
-// Launch shape override for tests and measurements: 0 = choose by size, 1 = one CTA per row, 2 = cluster per row.
+// Launch shape override for tests and measurements: 0 = choose by size, 1 = one CTA per row, 2 = a cluster of eight per row.
 void ulc_topk_set_mode(int mode) { g_topk_mode = mode; }
 
 int ulc_topk(const float* scores, long long row_stride, const int32_t* lengths, int rows, int max_len,

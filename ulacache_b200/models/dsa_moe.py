@@ -321,6 +321,8 @@ class DsaMoeModel:
                                                 rank=rank, gen=gen, shard_gen=shard_gen, dense_tp=1 if self.dpa else tp,
                                                 q_replicated=self.owner_attention))
         self._ag_by_rows = {}
+        self.record_selections = None       # a list here makes every layer append its selected record IDs
+        self.last_logits = None
         if self.deterministic:
             # split-K sums partial products with fp32 atomics, in an order that varies from run to run
             layers = list(self._unique) + ([self.mtp["layer"]] if self.mtp else [])
@@ -496,6 +498,8 @@ class DsaMoeModel:
         sel = self._select(logits, batch)
         if self.deterministic:
             sel = torch.sort(sel, dim=1, descending=True).values.contiguous()
+        if self.record_selections is not None:
+            self.record_selections.append(sel.clone())          # (eager runs only: for oracles and traces)
 
         # ---- cache: residency + resolve, publish the new KV, attend
         self._mark("cache.plan+write")
@@ -668,6 +672,7 @@ class DsaMoeModel:
         if self.dpa:
             h8, hs = self._gather_rows([h8, hs], getattr(self, "ag_head", None))    # vocabulary is sharded
         logits = self.lm_head(h8, hs, self.status).float()
+        self.last_logits = logits                               # this rank's vocabulary shard, fp32
         val, idx = logits.max(dim=-1)
         idx = idx + self.rank * self.vocab_local if self.tp > 1 else idx
         if self.tp > 1:

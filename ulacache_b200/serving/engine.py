@@ -118,11 +118,13 @@ class DecodeEngine:
         self._ids = None
 
     # ------------------------------------------------------------------- fill --
-    def fill_synthetic(self, chunk: int = 32768, seed: int = 1):
+    def fill_synthetic(self, chunk: int = 32768, seed: int = 1, on_chunk=None):
         """Admit ``batch`` requests with ``prompt_len`` cached tokens each: allocate their
         logical IDs, then write random KV records and index keys for every layer through
         the cache's own writers (the decode measurement starts from a full cache, as a
-        restore from a KV snapshot would leave it)."""
+        restore from a KV snapshot would leave it).  ``on_chunk(layer, first, last, latent, rope,
+        index_key)`` sees what was written for tokens ``first..last`` of the request-major token list
+        (for oracles that keep their own copy of the history)."""
         import torch
         from ..ops import records
 
@@ -137,6 +139,7 @@ class DecodeEngine:
                 raise MemoryError("index pool too small for the allocated pages")
             self.batch.req_pages[r] = pages
             all_ids.append(ids[: self.prompt_len])
+        self.request_ids = all_ids                       # logical record IDs of every request's prompt, in order
         self.batch.lengths.fill_(self.prompt_len)
         self.batch.tokens.copy_(torch.randint(0, self.cfg.vocab, (g.batch,), device=self.device, generator=gen).to(torch.int32))
         ids = torch.cat(all_ids)
@@ -151,6 +154,8 @@ class DecodeEngine:
                 k = torch.randn(e - s, 128, device=self.device, generator=gen, dtype=torch.bfloat16)
                 records.index_key_store(self.model.index_views[layer], k, ids[s:e], owner_only=True,
                                         status=self.model.status)
+                if on_chunk is not None:
+                    on_chunk(layer, s, e, lat, rope, k)
         torch.cuda.synchronize()
         self.cache.check("synthetic fill")
 
