@@ -173,6 +173,15 @@ def main():
     ap.add_argument("--layers", type=int, default=0, help="debug only: fewer layers (marks the result invalid)")
     ap.add_argument("--weight-budget-gb", type=float, default=0.0,
                     help="HBM for weights per rank; 0 = what 180 GB leaves after the KV and index pools (at most 125)")
+    ap.add_argument("--host-fraction", type=float, default=0.0,
+                    help="fraction of every rank's KV records kept in pinned host memory instead of HBM: the "
+                         "residency transaction (pin / plan / exchange over PCIe / commit) then runs in every layer "
+                         "of every timed step")
+    ap.add_argument("--kv-budget-hbm-gb", type=float, default=64.0,
+                    help="per-rank HBM budget for KV + index + cache metadata used for the capacity figure "
+                         "(what 180 GB leave beside 101 GB of weights at 8 GPUs)")
+    ap.add_argument("--kv-budget-host-gb", type=float, default=128.0,
+                    help="per-rank pinned host budget for KV used for the capacity figure (the reference's setting)")
     ap.add_argument("--no-graph", action="store_true")
     ap.add_argument("--comm", default="peer", choices=["peer", "nccl"],
                     help="cross-rank reductions: fused peer stores (default) or library all-reduce (baseline)")
@@ -221,8 +230,17 @@ def main():
         cfg = DsaMoeConfig(layers=cfg.layers, unique_layer_weights=unique, mtp_layers=mtp)
     global_batch = args.batch_per_gpu * world
     batch = global_batch if args.mode == "tp" else args.batch_per_gpu
+    tiers = {}
+    if args.host_fraction > 0:
+        kv_ranks = world if args.mode == "tp" else 1
+        span = 64 * kv_ranks
+        rows_per_request = args.spec_steps + 1 if mtp else 1
+        total = (args.prompt_len + max_new * rows_per_request + rows_per_request + span - 1) // span * span
+        needed = (batch * total // kv_ranks + 64 + 63) // 64 * 64
+        device = max(64, int(needed * (1.0 - args.host_fraction)) // 64 * 64)
+        tiers = dict(device_record_capacity=device, host_record_capacity=needed - device + 64)
     eng = DecodeEngine(cfg, batch=batch, prompt_len=args.prompt_len, max_new_tokens=max_new, mode=args.mode,
-                       rank=rank, world=world, local_rank=local, group=group, cpu_group=cpu_group,
+                       rank=rank, world=world, local_rank=local, group=group, cpu_group=cpu_group, **tiers,
                        use_graph=not args.no_graph, comm=args.comm, spec_steps=args.spec_steps,
                        force_accept=None if args.spec_accept == "model" else int(args.spec_accept),
                        tp_attention=args.tp_attention)
@@ -268,10 +286,12 @@ def main():
 
     for _ in range(warmup):
         eng.step_device()
+    tier0 = eng.cache.counters() if tiers else None
     e0 = emitted()
     with ClockSampler(local) as clocks:
         ms_dev = timed(eng.step_device, steps)
     e1 = emitted()
+    tier1 = eng.cache.counters() if tiers else None
     eng.check()
     eng.host_in.copy_(eng.batch.out_tokens.cpu())
     for _ in range(2):
@@ -315,6 +335,18 @@ def main():
             for _ in range(2):
                 eng.step_device()
         barrier()
+    # "KV tokens admitted at a fixed budget": the capacity planner's answer for the stated per-rank
+    # byte budgets (payload, index pages, directories and recency metadata all priced), times the ranks
+    from ulacache_b200.storage.capacity import CacheMemoryBudget, plan_cache_capacity, simple_usage_model
+
+    usage = simple_usage_model(record_bytes=656, layers=cfg.cache_layers, index_layers=cfg.cache_layers,
+                               metadata_groups=cfg.cache_layers)
+    cap = plan_cache_capacity(memory_budget=CacheMemoryBudget(int(args.kv_budget_hbm_gb * 1e9), int(args.kv_budget_host_gb * 1e9)),
+                              measure_memory_usage=usage, minimum_device_token_capacity=64 * 64,
+                              maximum_token_capacity_per_owner=(1 << 31) // 64 * 64 - 64)
+    hbm_only = plan_cache_capacity(memory_budget=CacheMemoryBudget(int(args.kv_budget_hbm_gb * 1e9), 0),
+                                   measure_memory_usage=usage, minimum_device_token_capacity=64 * 64,
+                                   maximum_token_capacity_per_owner=(1 << 31) // 64 * 64 - 64)
     if rank == 0:
         tok_s = tok_dev / (ms_dev / 1e3)
         e2e_tok_s = tok_e2e / (ms_e2e / 1e3)
@@ -345,11 +377,19 @@ def main():
                                         "tokens_per_request_step": round(tok_dev / max(1, global_batch * steps), 3)}
                                        if args.spec_steps else None),
                        "kv_records_per_rank": mem["kv_records_per_rank"],
-                       "kv_tokens_admitted": global_batch * (args.prompt_len + max_new),
+                       "kv_tokens_resident_in_this_run": global_batch * (args.prompt_len + max_new),
+                       "kv_tokens_admitted": (cap.device_token_capacity_per_owner + cap.host_token_capacity_per_owner) * world,
+                       "kv_capacity": {"budget_per_rank_gb": {"hbm": args.kv_budget_hbm_gb, "host": args.kv_budget_host_gb},
+                                       "device_tokens_per_rank": cap.device_token_capacity_per_owner,
+                                       "host_tokens_per_rank": cap.host_token_capacity_per_owner,
+                                       "tokens_hbm_only": hbm_only.device_token_capacity_per_owner * world,
+                                       "requests_of_this_length": (cap.device_token_capacity_per_owner
+                                                                   + cap.host_token_capacity_per_owner) * world
+                                       // (args.prompt_len + 1024)},
                        "weights_gb_per_rank": round(mem["weights_bytes"] / 1e9, 2),
                        "kv_gb_per_rank": round(mem["kv_bytes"] / 1e9, 2),
                        "switches": {k: os.environ[k] for k in ("ULC_DETERMINISTIC", "ULC_DENSE_ROWS_HINT",
-                                                                "ULC_MOE_SHARED_PLACEMENT") if k in os.environ},
+                                                                "ULC_MOE_SHARED_PLACEMENT", "ULC_TOPK_FUSED") if k in os.environ},
                        "valid": not args.layers},
             "hbm_floor_ms": round(floor_ms, 3), "fraction_of_floor": round(floor_ms / (ms_dev / steps), 3),
             "hbm_floor": {"bandwidth_gbs": hbm_gbs, "bandwidth_source": hbm_src,
@@ -363,6 +403,16 @@ def main():
                     "h2d_bytes_per_step": batch * 4, "d2h_bytes_per_step": batch * 4},
             "gpu_launches": eng.launches_per_step * steps,
         }
+        if tiers:
+            d = {k: tier1[k] - tier0[k] for k in ("hits", "misses", "promotions", "evictions", "unserved")}
+            line["host_tier"] = {
+                "host_records_per_rank": mem["host_records_per_rank"], "device_records_per_rank": mem["kv_records_per_rank"],
+                "host_fraction": args.host_fraction,
+                "promotions_per_step": d["promotions"] / steps, "evictions_per_step": d["evictions"] / steps,
+                "hit_rate": round(d["hits"] / max(1, d["hits"] + d["misses"]), 4), "unserved": d["unserved"],
+                "pcie_gb_per_s": round((d["promotions"] + d["evictions"]) * 656 / (ms_dev / 1e3) / 1e9, 2),
+                "note": "rank 0's counters over the timed steps; selections of a random-init indexer have no "
+                        "temporal locality, so the hit rate is about 1 - host_fraction"}
         print(json.dumps(line))
     eng.close()
     if world > 1:

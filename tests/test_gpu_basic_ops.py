@@ -25,6 +25,28 @@ def test_gemm_matches_reference(native, T, Nout, K, splits):
     assert err <= 0.02 * ref.abs().max().item() + 1e-2, err
 
 
+@pytest.mark.parametrize("T,heads", [(5, 3), (32, 16), (48, 128), (130, 4)])
+def test_batched_gemm_with_quantising_epilogue(native, T, heads):
+    """Per-head product whose epilogue quantises each head's 128 outputs as one fp8 group."""
+    from ulacache_b200.ops import fp8
+
+    torch.manual_seed(T + heads)
+    x = torch.randn(T, heads, 512, device="cuda", dtype=torch.bfloat16)
+    w = (torch.randn(heads, 128, 512, device="cuda") * 0.05).to(torch.bfloat16)
+    status = N.new_status("cuda")
+    q, sc = gemm.batched_linear_quant(x, w, status=status)
+    torch.cuda.synchronize()
+    N.raise_on_status(status, "gemm")
+    ref = torch.einsum("tbk,bnk->tbn", x.float(), w.float()).reshape(T, heads * 128)
+    want_q, want_s = fp8.act_quant_reference(ref)
+    assert torch.allclose(sc, want_s, rtol=2e-3, atol=1e-6)
+    got = q.view(torch.float8_e4m3fn).float().view(T, heads, 128) * sc.view(T, heads, 1)
+    want = want_q.view(torch.float8_e4m3fn).float().view(T, heads, 128) * want_s.view(T, heads, 1)
+    # one fp8 step (2^-3 relative) at most where the fp32 sums differ in the last bits
+    assert (got - want).abs().max().item() <= 0.13 * want.abs().max().item()
+    assert ((got - want).abs() > 1e-3 * want.abs().max()).float().mean().item() < 0.02
+
+
 @pytest.mark.parametrize("mode", ["row", "cluster"])
 @pytest.mark.parametrize("rows,Lmax,k", [(3, 100, 128), (4, 5000, 256), (2, 131072, 2048), (5, 40000, 2048),
                                          (32, 32768, 2048)])
@@ -76,6 +98,28 @@ def test_topk_ties_and_transform(native, mode):
     ref = topk.topk_reference(s, 512, xform=table)
     for r in range(2):
         assert sorted(out[r].tolist()) == sorted(ref[r].tolist())
+
+
+@pytest.mark.parametrize("rows,Lmax,k", [(3, 100, 128), (4, 5000, 256), (2, 131072, 2048), (5, 40000, 2048),
+                                         (32, 32768, 2048), (130, 9000, 2048)])
+def test_topk_histogram_method_matches_reference(native, rows, Lmax, k):
+    """Histogram launch + selection launch through the global workspace (no clusters), twice in a row
+    on the same workspace."""
+    torch.manual_seed(3)
+    for trial in range(2):
+        s = torch.randn(rows, Lmax, device="cuda") if trial == 0 else 1.0 + 0.2 * torch.rand(rows, Lmax, device="cuda")
+        if trial == 1:
+            s[-1] = 1.5                                  # every element tied: lowest positions win
+        lengths = torch.randint(max(1, Lmax // 2), Lmax + 1, (rows,), device="cuda", dtype=torch.int32)
+        vals = torch.empty(rows, k, device="cuda")
+        out = topk.topk(s, k, lengths, out_val=vals, method="hist")
+        torch.cuda.synchronize()
+        ref = topk.topk_reference(s, k, lengths)
+        for r in range(rows):
+            assert sorted(out[r].tolist()) == sorted(ref[r].tolist()), (trial, r)
+            picked = out[r][out[r] >= 0].long()
+            assert torch.equal(vals[r][out[r] >= 0], s[r][picked])
+        assert topk.workspace_is_clean(topk.workspace(rows, "cuda"), rows)
 
 
 def _single_rank_view(pool, directory, rec_bytes):

@@ -120,3 +120,30 @@ def test_gemm_reduce_scatter_epilogue(native):
     N.raise_on_status(status, "gemm reduce-scatter")
     for r in range(3):
         assert torch.equal(bufs[r], want[r * per:(r + 1) * per])
+
+
+@pytest.mark.parametrize("M,Nout,K,splits", [(32, 2304, 7168, 8), (32, 7168, 16384, 5), (7, 128, 7168, 4),
+                                              (16, 512, 2048, 16), (20, 384, 1024, 3)])
+def test_dense_split_k_reduced_in_the_kernel(native, M, Nout, K, splits):
+    """K splits of a dense decode GEMM: partial tiles meet in the workspace, the last split of each
+    tile sums them.  Twice on the same workspace (the tickets reset themselves), also with the result
+    sent to 'peer' buffers."""
+    torch.manual_seed(M + K)
+    x = torch.randn(M, K, device="cuda", dtype=torch.bfloat16)
+    w = torch.randn(Nout, K, device="cuda") * 0.05
+    x8, sx = fp8.act_quant(x)
+    w8, sw = fp8.quantize_weight(w)
+    wt = fp8.tile_weight(w8)
+    status = N.new_status("cuda")
+    ref = fp8.grouped_gemm_reference(x8, sx, w8, sw)
+    for trial in range(2):
+        y = fp8.grouped_gemm(x8, sx, wt, sw, splits=splits, status=status)
+        torch.cuda.synchronize()
+        N.raise_on_status(status, "fp8 gemm")
+        assert (y.float() - ref).abs().max().item() <= 0.01 * ref.abs().max().item() + 1e-2
+    assert int(fp8.splitk_workspace("cuda")[:4096].view(torch.int32).abs().sum()) == 0
+    bufs = [torch.zeros(M, Nout, device="cuda", dtype=torch.bfloat16) for _ in range(2)]
+    fp8.grouped_gemm(x8, sx, wt, sw, splits=splits, status=status, peer_out=[b.data_ptr() for b in bufs])
+    torch.cuda.synchronize()
+    N.raise_on_status(status, "fp8 gemm")
+    assert torch.equal(bufs[0], y) and torch.equal(bufs[1], y)

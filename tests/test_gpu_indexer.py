@@ -61,3 +61,37 @@ def test_select_topk_ids(native):
         assert len(got) == n
         overlap = len(set(got) & set(want)) / n
         assert overlap > 0.995        # fp8 accumulation order may flip near-ties at the boundary
+
+
+@pytest.mark.parametrize("R,n_q,max_pages,ranks,rank,k", [(3, 1, 40, 1, 0, 512), (4, 1, 300, 1, 0, 2048),
+                                                         (2, 2, 64, 2, 1, 256), (2, 4, 40, 4, 2, 128)])
+def test_fused_histogram_select_matches_separate_kernels(native, R, n_q, max_pages, ranks, rank, k):
+    """The score kernel building the rows' histograms + the histogram-first select pick exactly the
+    records the separate score and select kernels pick, call after call on one workspace."""
+    from ulacache_b200.ops import topk as topk_op
+
+    torch.manual_seed(R * 7 + max_pages)
+    pages = 1024
+    pool = _index_pool(pages, 3)
+    q8, wf = indexer.quantize_queries(torch.randn(R, n_q, 64, 128, device="cuda"),
+                                      torch.randn(R, n_q, 64, device="cuda"))
+    page_table = torch.stack([torch.randperm(pages, device="cuda")[:max_pages] for _ in range(R)]).to(torch.int32)
+    full = max_pages * 64 * ranks
+    ws = topk_op.workspace(R * n_q, "cuda")
+    status = N.new_status("cuda")
+    for trial in range(3):
+        lengths = torch.randint(1, full + 1, (R,), device="cuda", dtype=torch.int32)
+        if trial == 0:
+            lengths[0] = full
+        if trial == 1:
+            lengths[-1] = min(full, k // 2)            # a row shorter than k: everything is selected
+        plain = indexer.index_score(q8, wf, page_table, lengths, pool, ranks=ranks, rank=rank, status=status)
+        want = indexer.select_topk(plain, k, page_table, n_q=n_q, ranks=ranks, rank=rank)
+        fused = indexer.index_score(q8, wf, page_table, lengths, pool, ranks=ranks, rank=rank, status=status,
+                                    topk_workspace=ws)
+        got = indexer.select_topk(fused, k, page_table, n_q=n_q, ranks=ranks, rank=rank, hist_workspace=ws)
+        torch.cuda.synchronize()
+        N.raise_on_status(status, "index_score")
+        for r in range(R * n_q):
+            assert sorted(got[r].tolist()) == sorted(want[r].tolist()), (trial, r)
+        assert topk_op.workspace_is_clean(ws, R * n_q)         # the select leaves histograms and counters zero

@@ -53,26 +53,36 @@ def test_decode_step_matches_dense_reference(native, monkeypatch, prompt):
     for step in range(steps):
         tokens = eng.batch.tokens.clone()
         positions = eng.batch.lengths.clone()
-        eng.model.record_selections = []
+        eng.model.record_selections, eng.model.record_routing = [], []
         eng.step_device()
         torch.cuda.synchronize()
         eng.check()
         got = eng.model.last_logits[:, : cfg.vocab].float()
         sels = [_positions_of(ids_by_request, s, span) for s in eng.model.record_selections]
-        eng.model.record_selections = None
-        assert len(sels) == cfg.layers
-        want = ref.step(tokens, positions, selections=sels)
+        routing = eng.model.record_routing
+        eng.model.record_selections = eng.model.record_routing = None
+        assert len(sels) == cfg.layers and len(routing) == cfg.layers - cfg.dense_layers
+        want = ref.step(tokens, positions, selections=sels, routing=routing)
+        # (fp8 activations turn last-bit differences of accumulation order into whole quantisation steps,
+        # so the composed logits agree to a few per cent; a wrong wiring shows as tens of per cent)
+        # the kernels' experts are the oracle's own choice, up to near-ties of the (random-init) router
+        for (choice, gate), (scores, own) in zip(routing, ref.routing):
+            picked = torch.gather(scores, 1, choice.long())
+            kth = torch.gather(scores, 1, own)[:, -1:]
+            assert bool((picked >= kth - 2e-2).all())            # router logits are bf16
+            g = picked / picked.sum(-1, keepdim=True) * cfg.routed_scale
+            assert torch.allclose(gate, g, rtol=2e-2, atol=1e-3)
         err = (got - want).abs().max().item()
         scale = want.abs().max().item()
         worst = max(worst, err / scale)
-        assert err <= 0.03 * scale + 1e-3, (step, err, scale)
+        assert err <= 0.08 * scale + 1e-3, (step, err, scale)
         # greedy tokens agree unless the oracle's two best logits are within the tolerance
         top2 = torch.topk(want, 2, dim=-1).values
         gap = (top2[:, 0] - top2[:, 1])
         same = eng.batch.out_tokens.long() == want.argmax(dim=-1)
-        assert bool((same | (gap <= 0.03 * scale)).all()), (step, eng.batch.out_tokens.tolist(), want.argmax(-1).tolist())
+        assert bool((same | (gap <= 0.08 * scale)).all()), (step, eng.batch.out_tokens.tolist(), want.argmax(-1).tolist())
         mismatched += int((~same).sum())
-    assert mismatched <= 2, mismatched
+    assert mismatched <= steps * B // 4, mismatched        # (a tiny random-init model has many near-tied logits)
     eng.close()
 
 

@@ -160,14 +160,21 @@ def bench_topk(mods, timer, rows_list, ctx_list, k=2048):
             def our_call():
                 ours.topk(scores, k, lens, out=out_ours)
 
-            ref_call(); our_call()
+            out_hist = torch.empty_like(out_ours)
+
+            def our_hist_call():
+                ours.topk(scores, k, lens, out=out_hist, method="hist")
+
+            ref_call(); our_call(); our_hist_call()
             torch.cuda.synchronize()
             a = torch.sort(out_ref.long(), dim=1).values
             b = torch.sort(out_ours.long(), dim=1).values
-            same = bool((a == b).all())
-            t_ref, t_ours = timer(ref_call), timer(our_call)
-            res.append({"rows": rows, "ctx": ctx, "k": k, "reference_us": round(t_ref, 2), "ours_us": round(t_ours, 2),
-                        "speedup": round(t_ref / t_ours, 3), "same_selection": same})
+            c = torch.sort(out_hist.long(), dim=1).values
+            same = bool((a == b).all()) and bool((a == c).all())
+            t_ref, t_ours, t_hist = timer(ref_call), timer(our_call), timer(our_hist_call)
+            res.append({"rows": rows, "ctx": ctx, "k": k, "reference_us": round(t_ref, 2), "ours_cluster_us": round(t_ours, 2),
+                        "ours_hist_us": round(t_hist, 2), "speedup": round(t_ref / min(t_ours, t_hist), 3),
+                        "same_selection": same})
             print(json.dumps(res[-1]), file=sys.stderr)
     return res
 

@@ -41,14 +41,17 @@ struct F8Geom {
   // is the critical stage of the pipeline there, and a shared-memory read per token and K block is
   // cheaper than a global load, a multiply and a register move.
   static constexpr int kScaleBytes = MAXN <= 32 ? MAXN * 144 * 4 : 0;
+  // The finished bf16 tile [token][feature] of the pass, staged so that the global stores are
+  // 16-byte vectors along the feature axis issued by all epilogue threads.
+  static constexpr int kOutBytes = MAXN <= 32 ? MAXN * 128 * 2 : 0;
   // An EVEN number of stages: the two MMA issuers take alternate K blocks, and a stage must
   // always come back to the same issuer.  A thread that waited on only every other phase of a
   // stage's barrier could not tell "my phase completed" from "the phase before it is still
   // pending" (a parity wait distinguishes adjacent phases only).
-  static constexpr int kFit = (200 * 1024 - kPartBytes - kScaleBytes) / kStageBytes;
+  static constexpr int kFit = (200 * 1024 - kPartBytes - kScaleBytes - kOutBytes) / kStageBytes;
   static constexpr int kStages = (kFit > 12 ? 12 : kFit) & ~1;
   static_assert(kStages >= 2 && kStages % 2 == 0, "stage count must be even");
-  static constexpr int kSmem = 1024 + kStages * kStageBytes + 512 + kPartBytes + kScaleBytes;
+  static constexpr int kSmem = 1024 + kStages * kStageBytes + 512 + kPartBytes + kScaleBytes + kOutBytes;
   // The K slices of a block may be spread over kSlices independent TMEM accumulators
   // (summed by the epilogue) to break the accumulate-after-accumulate dependency.
   static constexpr int kSlices = 1;   // measured: more slices do not help, the issue rate of one thread does
@@ -67,6 +70,11 @@ struct F8Params {
   int n_peers;
   int32_t* status;
   int M, Nout, K, E, kb_per_split, splits, out_f32;
+  // In-kernel split-K reduction (dense layers, all rows in one pass): every split leaves its fp32
+  // partial tile in `part`, takes a ticket, and the last split of a tile to arrive sums them and
+  // stores bf16 - no cleared accumulation buffer, no global atomics, no conversion kernel.
+  float* part;                // [tiles * splits][MAXN][128] fp32 (nullable)
+  uint32_t* tickets;          // [tiles], zero when the kernel starts, zero again when it ends
   int rows_per_peer;          // > 0: reduce-scatter, row m goes only to peer m / rows_per_peer at row m % rows_per_peer
 };
 
@@ -77,6 +85,7 @@ struct F8Barriers {
   uint64_t acc_empty[kF8MaxAccBufs];
   uint32_t tmem_base;
   int abort_flag;
+  int reduce_last;            // split-K reduction: this CTA drew the last ticket of its tile
 };
 
 // Optional timeline of CTA 0, compiled in with -DULC_F8_TRACE (development only):
@@ -93,6 +102,7 @@ __device__ long long f8_trace[3][64][4];
 
 struct F8Item {
   int e, n0, kb0, nkb, m_begin, m_end;
+  int tile_id, split;         // (expert slot, feature tile) index and K split of the item
 };
 
 // Work item `idx` of the persistent loop: (active expert, feature tile, K split).
@@ -103,6 +113,8 @@ __device__ __forceinline__ F8Item f8_item(const F8Params& p, int idx) {
   const int a = idx / (p.splits * tiles);
   F8Item it;
   it.e = p.active ? p.active[a] : a;
+  it.tile_id = a * tiles + tile;
+  it.split = split;
   it.n0 = tile * kF8BM;
   const int KB = p.K / kF8BK;
   it.kb0 = split * p.kb_per_split;
@@ -147,6 +159,32 @@ fp8_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid
     ptx::prefetch_tmap(&tmap_x);
   }
   if (warp == 1) { ptx::tmem_alloc<512>(&bar.tmem_base); ptx::tmem_relinquish(); }
+  // Dense layers (one weight, no row offsets to look up): the scales of this CTA's first pass are
+  // requested NOW.  Once the producers of all CTAs have started, some 35 MB of weight tiles are
+  // queued in the memory system and a small load issued behind them waits microseconds; the
+  // epilogue cannot consume its first K block without these values.
+  constexpr int kPreJ = MAXN <= 32 ? MAXN / 8 : 1;
+  float pre_sx[kPreJ][2], pre_sw[2];
+  bool pre_valid = false;
+  if constexpr (MAXN <= 32) {
+    if (p.E == 1 && warp >= 2 && warp != kF8SecondMmaWarp) {
+      const F8Item w0 = f8_item(p, blockIdx.x);
+      const int nt0 = min(kF8MaxN, w0.m_end - w0.m_begin);
+      const float* sxb = p.sx + static_cast<size_t>(w0.m_begin) * KB + w0.kb0;
+      const float* swt = p.sw + (static_cast<size_t>(w0.e) * (p.Nout / kF8BM) + w0.n0 / kF8BM) * KB + w0.kb0;
+#pragma unroll
+      for (int ii = 0; ii < 2; ++ii) {
+        const int i = lane + 32 * ii;
+        pre_sw[ii] = i < w0.nkb ? swt[i] : 0.f;
+#pragma unroll
+        for (int jj = 0; jj < kPreJ; ++jj) {
+          const int j = (warp - 2) + 8 * jj;
+          pre_sx[jj][ii] = (i < w0.nkb && j < nt0) ? sxb[static_cast<size_t>(j) * KB + i] : 0.f;
+        }
+      }
+      pre_valid = true;
+    }
+  }
   ptx::tc_fence_before();
   __syncthreads();
   ptx::tc_fence_after();
@@ -238,6 +276,7 @@ fp8_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid
     const int colh = kAlternate ? 0 : grp;
     float* s_part = reinterpret_cast<float*>(smem + kF8Stages * kF8StageBytes + 512);   // [128][MAXN] when alternating
     float* s_scale = s_part + 128 * (kAlternate ? MAXN : 0);                             // [MAXN][kF8MaxKB] when alternating
+    __nv_bfloat16* s_out = reinterpret_cast<__nv_bfloat16*>(s_scale + (kAlternate ? MAXN * kF8MaxKB : 0));   // [MAXN][128]
     const int etid = ew * 32 + lane;                                                     // 0..255 over the epilogue warps
     int it = 0;
     for (int idx = blockIdx.x; idx < n_items && !*abort_flag; idx += gridDim.x) {
@@ -258,9 +297,19 @@ fp8_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid
         const float* sx_base = p.sx + static_cast<size_t>(t0 + colh * 64) * KB + w.kb0;
         if (kAlternate) {
           // (both groups have left the previous pass: its closing barriers are behind every warp)
-          for (int q = etid; q < MAXN * w.nkb; q += 256) {
-            const int j = q / w.nkb, i = q - j * w.nkb;
-            s_scale[j * kF8MaxKB + i] = j < nt ? sx_base[static_cast<size_t>(j) * KB + i] * sw_tile[i] : 0.f;
+          // a warp per token row, a lane per K block: every load of the table is independent of the
+          // others and in flight at once (the epilogue cannot consume a block before its products exist)
+          const bool from_regs = pre_valid && idx == static_cast<int>(blockIdx.x) && ps == 0;
+#pragma unroll
+          for (int jj = 0; jj < MAXN / 8; ++jj) {
+            const int j = ew + 8 * jj;
+            if (from_regs) {
+#pragma unroll
+              for (int ii = 0; ii < 2; ++ii)
+                if (lane + 32 * ii < w.nkb) s_scale[j * kF8MaxKB + lane + 32 * ii] = pre_sx[jj < kPreJ ? jj : 0][ii] * pre_sw[ii];
+            }
+            for (int i = lane + (from_regs ? 64 : 0); i < w.nkb; i += 32)
+              s_scale[j * kF8MaxKB + i] = j < nt ? sx_base[static_cast<size_t>(j) * KB + i] * sw_tile[i] : 0.f;
           }
           asm volatile("bar.sync 3, 256;" ::: "memory");
           if (etid == 0) F8_T(2, (idx - blockIdx.x) / gridDim.x, 1);   // scale table ready
@@ -332,19 +381,90 @@ fp8_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid
         if (etid == 0) F8_T(2, (idx - blockIdx.x) / gridDim.x, 2);     // last K block consumed
         if (kAlternate) {
           // group 1 parks its partial sums, group 0 adds them and stores
+          // (token-major staging: the 32 lanes of a warp hold 32 consecutive features, so every
+          // shared-memory access below is conflict free)
           const int row = qd * 32 + lane;
           if (grp == 1) {
 #pragma unroll
-            for (int j = 0; j < kAcc; ++j) s_part[row * kAcc + j] = acc[j];
+            for (int j = 0; j < kAcc; ++j) s_part[j * 128 + row] = acc[j];
           }
           asm volatile("bar.sync 1, 256;" ::: "memory");
           if (grp == 0) {
 #pragma unroll
-            for (int j = 0; j < kAcc; ++j) acc[j] += s_part[row * kAcc + j];
+            for (int j = 0; j < kAcc; ++j) acc[j] += s_part[j * 128 + row];
+            if (p.part != nullptr) {
+#pragma unroll
+              for (int j = 0; j < kAcc; ++j) s_part[j * 128 + row] = acc[j];
+            } else if (!p.out_f32) {
+#pragma unroll
+              for (int j = 0; j < kAcc; ++j) s_out[j * 128 + row] = __float2bfloat16(acc[j]);
+            }
           }
           asm volatile("bar.sync 2, 256;" ::: "memory");    // s_part may be rewritten by the next pass
+          if (p.part != nullptr) {
+            // split-K: park the fp32 partial tile, take a ticket; the last split of the tile reduces
+            const size_t slot = (static_cast<size_t>(w.tile_id) * p.splits + w.split) * (MAXN * 128);
+            const float4* src4 = reinterpret_cast<const float4*>(s_part);
+            float4* dst4 = reinterpret_cast<float4*>(p.part + slot);
+            for (int u = etid; u < nt * 32; u += 256) __stcg(dst4 + u, src4[u]);
+            __threadfence();
+            asm volatile("bar.sync 3, 256;" ::: "memory");   // every partial of this CTA is out; s_part is free again
+            if (etid == 0) {
+              const uint32_t ticket = atomicAdd(p.tickets + w.tile_id, 1u);
+              bar.reduce_last = ticket == static_cast<uint32_t>(p.splits - 1) ? 1 : 0;
+              if (bar.reduce_last) p.tickets[w.tile_id] = 0;      // ready for the next launch
+            }
+            asm volatile("bar.sync 3, 256;" ::: "memory");
+            if (bar.reduce_last) {
+              __threadfence();
+              const float4* base4 = reinterpret_cast<const float4*>(p.part + static_cast<size_t>(w.tile_id) * p.splits * (MAXN * 128));
+              for (int u = etid; u < nt * 32; u += 256) {
+                float4 sum = make_float4(0.f, 0.f, 0.f, 0.f);
+                for (int sp = 0; sp < p.splits; ++sp) {
+                  const float4 v = __ldcg(base4 + static_cast<size_t>(sp) * (MAXN * 32) + u);
+                  sum.x += v.x; sum.y += v.y; sum.z += v.z; sum.w += v.w;
+                }
+                const __nv_bfloat162 lo = __floats2bfloat162_rn(sum.x, sum.y), hi = __floats2bfloat162_rn(sum.z, sum.w);
+                uint2 pk;
+                pk.x = *reinterpret_cast<const uint32_t*>(&lo);
+                pk.y = *reinterpret_cast<const uint32_t*>(&hi);
+                const int r = u >> 5, c4 = u & 31;
+                const int grow = t0 + r;
+                const size_t o = static_cast<size_t>(grow) * p.Nout + w.n0 + c4 * 4;
+                if (p.out) *reinterpret_cast<uint2*>(reinterpret_cast<__nv_bfloat16*>(p.out) + o) = pk;
+                if (p.rows_per_peer > 0) {
+                  const int pr = grow / p.rows_per_peer;
+                  if (pr < p.n_peers)
+                    *reinterpret_cast<uint2*>(reinterpret_cast<__nv_bfloat16*>(p.out_peers[pr]) +
+                                              static_cast<size_t>(grow % p.rows_per_peer) * p.Nout + w.n0 + c4 * 4) = pk;
+                } else {
+                  for (int pr = 0; pr < p.n_peers; ++pr)
+                    *reinterpret_cast<uint2*>(reinterpret_cast<__nv_bfloat16*>(p.out_peers[pr]) + o) = pk;
+                }
+              }
+            }
+          } else if (!p.out_f32) {
+            // all 256 epilogue threads store the tile: 16 bytes (8 features) per thread and step
+            const uint4* src = reinterpret_cast<const uint4*>(s_out);
+            for (int u = etid; u < nt * 16; u += 256) {
+              const int r = u >> 4, c = u & 15;
+              const uint4 v = src[u];
+              const int grow = t0 + r;
+              const size_t o = static_cast<size_t>(grow) * p.Nout + w.n0 + c * 8;
+              if (p.out) *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(p.out) + o) = v;
+              if (p.rows_per_peer > 0) {
+                const int pr = grow / p.rows_per_peer;
+                if (pr < p.n_peers)
+                  *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(p.out_peers[pr]) +
+                                            static_cast<size_t>(grow % p.rows_per_peer) * p.Nout + w.n0 + c * 8) = v;
+              } else {
+                for (int pr = 0; pr < p.n_peers; ++pr)
+                  *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(p.out_peers[pr]) + o) = v;
+              }
+            }
+          }
         }
-        if (f < p.Nout && (!kAlternate || grp == 0)) {
+        if (f < p.Nout && ((!kAlternate) || (grp == 0 && p.out_f32 && p.part == nullptr))) {
 #pragma unroll
           for (int j = 0; j < kAcc; ++j) {
             if (j < my_n) {
@@ -482,7 +602,7 @@ int ulc_fp8_grouped_gemm(const void* x8, const float* sx, const void* w8, const 
 static int f8_gemm_impl(const void* x8, const float* sx, const void* w8, const float* sw, const int32_t* offs,
                        int M, int Nout, int K, int E, int splits, int max_rows, void* y, void* const* peer_out,
                        int n_peers, int rows_per_peer, int32_t* work, int32_t* status, cudaStream_t stream,
-                       bool work_ready = false) {
+                       bool work_ready = false, void* splitk_ws = nullptr, long long splitk_ws_bytes = 0) {
   if (M <= 0 || E <= 0) return 0;
   if ((K % 128) || (Nout % 128) || K / 128 > kF8MaxKB) return -kErrUnsupported;
   if (E > 1 && (offs == nullptr || work == nullptr)) return -kErrUnsupported;
@@ -501,13 +621,26 @@ static int f8_gemm_impl(const void* x8, const float* sx, const void* w8, const f
   F8Params p;
   p.sw = sw; p.sx = sx; p.offs = offs; p.out = y; p.status = status;
   p.M = M; p.Nout = Nout; p.K = K; p.E = E;
-  if (n_peers < 0 || n_peers > 8 || (n_peers > 0 && splits > 1)) return -kErrUnsupported;
+  if (n_peers < 0 || n_peers > 8 || (n_peers > 0 && splits > 1 && splitk_ws == nullptr)) return -kErrUnsupported;
   p.n_peers = n_peers;
   for (int r = 0; r < 8; ++r) p.out_peers[r] = r < n_peers ? peer_out[r] : nullptr;
   const int KB = K / 128;
   p.kb_per_split = (KB + splits - 1) / splits;
   p.splits = (KB + p.kb_per_split - 1) / p.kb_per_split;
   p.out_f32 = splits > 1;
+  p.part = nullptr;
+  p.tickets = nullptr;
+  if (max_rows <= 0 || max_rows > M) max_rows = M;
+  if (splitk_ws != nullptr && p.splits > 1) {
+    // tickets (one per feature tile, 4 KB reserved) then the partial tiles
+    const int geom = max_rows <= 16 ? 16 : 32;
+    const long long tiles = Nout / kF8BM;
+    const long long need = 4096 + tiles * p.splits * geom * 128 * 4;
+    if (E != 1 || M > geom || max_rows > 32 || tiles > 1024 || need > splitk_ws_bytes) return -kErrUnsupported;
+    p.tickets = reinterpret_cast<uint32_t*>(splitk_ws);
+    p.part = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(splitk_ws) + 4096);
+    p.out_f32 = 0;
+  }
   p.active = nullptr;
   p.n_active = nullptr;
   p.rows_per_peer = rows_per_peer;
@@ -519,7 +652,6 @@ static int f8_gemm_impl(const void* x8, const float* sx, const void* w8, const f
   }
   const long long max_items = static_cast<long long>(E) * (Nout / kF8BM) * p.splits;
   const int grid = static_cast<int>(max_items < sm_count ? max_items : sm_count);
-  if (max_rows <= 0 || max_rows > M) max_rows = M;
   if (max_rows <= 16) return launch_f8<16>(tw, tx, p, grid, stream);
   if (max_rows <= 32) return launch_f8<32>(tw, tx, p, grid, stream);
   if (max_rows <= 64) return launch_f8<64>(tw, tx, p, grid, stream);
@@ -540,6 +672,19 @@ int ulc_fp8_grouped_gemm_prepared(const void* x8, const float* sx, const void* w
                                   cudaStream_t stream) {
   if (E <= 1 || work == nullptr) return -kErrUnsupported;
   return f8_gemm_impl(x8, sx, w8, sw, offs, M, Nout, K, E, 1, max_rows, y, nullptr, 0, 0, work, status, stream, true);
+}
+
+// Dense split-K GEMM with the reduction inside the kernel: y (bf16 [M, Nout], nullable) and/or the
+// peer buffers get the finished result; `workspace` (device memory, `ws_bytes` long, at least
+// 4096 + (Nout / 128) * splits * 32 * 128 * 4 bytes, its first 4096 bytes zero before the first use)
+// holds the partial tiles and the tickets and is left ready for the next call.  M <= 32.  Calls that
+// share a workspace must not overlap on the GPU.
+int ulc_fp8_gemm_splitk(const void* x8, const float* sx, const void* w8, const float* sw, int M, int Nout, int K,
+                        int splits, int max_rows, void* y, void* const* peer_out, int n_peers, int rows_per_peer,
+                        void* workspace, long long ws_bytes, int32_t* status, cudaStream_t stream) {
+  if (workspace == nullptr) return -kErrUnsupported;
+  return f8_gemm_impl(x8, sx, w8, sw, nullptr, M, Nout, K, 1, splits, max_rows, y, peer_out, n_peers, rows_per_peer,
+                      nullptr, status, stream, false, workspace, ws_bytes);
 }
 
 // GEMM + reduce-scatter: as ulc_fp8_grouped_gemm_peers (one weight), but row m of the result is

@@ -29,15 +29,19 @@ struct GemmSmem {
   static constexpr int kBBytes = BN * 128;
   static constexpr int kStageBytes = kABytes + kBBytes;
   static constexpr int kStages = (200 * 1024 / kStageBytes) > 8 ? 8 : (200 * 1024 / kStageBytes);
-  static constexpr int kBytes = kStages * kStageBytes + 1024 /*align*/ + 256 /*barriers*/;
+  static constexpr int kBytes = kStages * kStageBytes + 1024 /*align*/ + 256 /*barriers*/ + 4 * BN * 4 /*row maxima*/;
 };
 
-// out_mode 0: bf16 Y[T, N] plain store; 1: fp32 red.add into Y32[T, N] (split-K)
+// out_mode 0: bf16 Y[T, N] plain store; 1: fp32 red.add into Y32[T, N] (split-K);
+// 2: fp8 e4m3 bytes Y8 with one fp32 scale per (token, 128-feature tile) in `out_scale`
+//    [T, lds] at column batch * (N / 128) + tile: the activation quantiser of the next fp8 GEMM
+//    folded into this epilogue (a tile of 128 output features is exactly one quantisation group).
 template <int BN>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_wt_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_x,
                void* __restrict__ out, int T, int N, int K, int kb_per_split, int out_mode, int splits,
-               long long ldy, long long y_bstride, int stages, int32_t* status) {
+               long long ldy, long long y_bstride, int stages, int32_t* status, float* __restrict__ out_scale,
+               long long lds) {
   using S = GemmSmem<BN>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
@@ -137,7 +141,45 @@ gemm_wt_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
     }
     ptx::tc_fence_after();
     const int f = m0 + q * 32 + lane;
-    if (ok && !*abort_flag && num_kb > 0) {
+    if (out_mode == 2) {
+      // pass 1: per token the largest magnitude over this CTA's 128 features (warp, then the four warps)
+      float* s_amax = reinterpret_cast<float*>(smem + stages * S::kStageBytes + 256);        // [4][BN]
+      const bool live = ok && !*abort_flag && num_kb > 0;
+#pragma unroll
+      for (int c = 0; c < BN; c += 16) {
+        uint32_t r[16];
+        if (live) { ptx::tmem_ld16(tmem_d + (static_cast<uint32_t>(q * 32) << 16) + c, r); ptx::tmem_ld_wait(); }
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+          const uint32_t mag = (live && f < N) ? (r[j] & 0x7fffffffu) : 0u;       // |x| orders like its bit pattern
+          const uint32_t m = __reduce_max_sync(0xffffffffu, mag);
+          if (lane == 0) s_amax[q * BN + c + j] = __uint_as_float(m);
+        }
+      }
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      if (live) {
+#pragma unroll
+        for (int c = 0; c < BN; c += 16) {
+          uint32_t r[16];
+          ptx::tmem_ld16(tmem_d + (static_cast<uint32_t>(q * 32) << 16) + c, r);
+          ptx::tmem_ld_wait();
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            const int t = t0 + c + j;
+            if (t < T) {
+              const float amax = fmaxf(fmaxf(s_amax[c + j], s_amax[BN + c + j]),
+                                       fmaxf(s_amax[2 * BN + c + j], s_amax[3 * BN + c + j]));
+              const float scale = fmaxf(amax, 1e-4f) / 448.f;
+              if (f < N)
+                reinterpret_cast<uint8_t*>(out)[static_cast<size_t>(bz) * y_bstride + static_cast<size_t>(t) * ldy + f] =
+                    float_to_fp8_e4m3(__uint_as_float(r[j]) * (1.f / scale));
+              if (q == 0 && lane == 0)
+                out_scale[static_cast<size_t>(t) * lds + static_cast<size_t>(bz) * ((N + kGemmBM - 1) / kGemmBM) + blockIdx.x] = scale;
+            }
+          }
+        }
+      }
+    } else if (ok && !*abort_flag && num_kb > 0) {
 #pragma unroll
       for (int c = 0; c < BN; c += 16) {
         uint32_t r[16];
@@ -181,7 +223,7 @@ __global__ void cast_f32_bf16_kernel(const float* __restrict__ in, __nv_bfloat16
 template <int BN>
 static int launch_gemm(const CUtensorMap& tw, const CUtensorMap& tx, void* out, int T, int N, int K,
                        int splits, int out_mode, int batch, long long ldy, long long y_bstride, int32_t* status,
-                       cudaStream_t stream) {
+                       cudaStream_t stream, float* out_scale = nullptr, long long lds = 0) {
   using S = GemmSmem<BN>;
   static PerDeviceOnce once;
   const int attr_rc = ensure_dynamic_smem(reinterpret_cast<const void*>(gemm_wt_kernel<BN>), S::kBytes, once);
@@ -191,9 +233,11 @@ static int launch_gemm(const CUtensorMap& tw, const CUtensorMap& tx, void* out, 
   dim3 grid((N + kGemmBM - 1) / kGemmBM, (T + BN - 1) / BN, splits * batch);
   // no deeper a ring than the K blocks one CTA walks: the shared memory saved lets CTAs share an SM
   const int stages = kb_per_split < 2 ? 2 : (kb_per_split < S::kStages ? kb_per_split : S::kStages);
-  const size_t smem_bytes = static_cast<size_t>(stages) * S::kStageBytes + 1024 /*align*/ + 256 /*barriers*/;
+  const size_t smem_bytes = static_cast<size_t>(stages) * S::kStageBytes + 1024 /*align*/ + 256 /*barriers*/ +
+                            (out_mode == 2 ? 4 * BN * sizeof(float) : 0);
   gemm_wt_kernel<BN><<<grid, kGemmThreads, smem_bytes, stream>>>(tw, tx, out, T, N, K, kb_per_split,
-                                                                  out_mode, splits, ldy, y_bstride, stages, status);
+                                                                  out_mode, splits, ldy, y_bstride, stages, status,
+                                                                  out_scale, lds);
   return static_cast<int>(cudaGetLastError());
 }
 
@@ -262,6 +306,30 @@ int ulc_gemm_wt_bf16_batched(const void* x, const void* w, void* y, int T, int N
     r = static_cast<int>(cudaGetLastError());
   }
   return r;
+}
+
+// Batched GEMM whose result is quantised in the epilogue: for every b < batch,
+// Y8_b[T, N] = fp8(X_b W_b^T) with one fp32 scale per (token, 128 features), stored at
+// y8[t * ldy + b * y_bstride + n] (bytes) and scales[t * lds + b * ceil(N / 128) + n / 128].
+int ulc_gemm_wt_bf16_batched_quant(const void* x, const void* w, void* y8, float* scales, int T, int N, int K,
+                                   long long ldx, long long ldw, long long ldy, long long lds, int batch,
+                                   long long x_bstride, long long w_bstride, long long y_bstride, int32_t* status,
+                                   cudaStream_t stream) {
+  using namespace ulc;
+  if (T <= 0 || N <= 0 || K <= 0 || batch <= 0) return 0;
+  if ((K & 7) || (ldx & 7) || (ldw & 7)) return -kErrAlignment;
+  const int bn = T <= 16 ? 16 : T <= 32 ? 32 : T <= 64 ? 64 : 128;
+  CUtensorMap tw, tx;
+  int r = make_tmap_3d_bf16(&tw, w, N, K, batch, ldw, w_bstride, kGemmBM);
+  if (r != 0) return r;
+  r = make_tmap_3d_bf16(&tx, x, T, K, batch, ldx, x_bstride, bn);
+  if (r != 0) return r;
+  switch (bn) {
+    case 16: return launch_gemm<16>(tw, tx, y8, T, N, K, 1, 2, batch, ldy, y_bstride, status, stream, scales, lds);
+    case 32: return launch_gemm<32>(tw, tx, y8, T, N, K, 1, 2, batch, ldy, y_bstride, status, stream, scales, lds);
+    case 64: return launch_gemm<64>(tw, tx, y8, T, N, K, 1, 2, batch, ldy, y_bstride, status, stream, scales, lds);
+    default: return launch_gemm<128>(tw, tx, y8, T, N, K, 1, 2, batch, ldy, y_bstride, status, stream, scales, lds);
+  }
 }
 
 // Y[T,N] (bf16) = X[T,K] (bf16, row pitch ldx elements) * W[N,K]^T (bf16, row pitch ldw).

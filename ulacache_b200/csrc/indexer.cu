@@ -26,6 +26,7 @@
 #include "ulc/layout.h"
 #include "ulc/ptx.cuh"
 #include "ulc/tmap.h"
+#include "ulc/topk_key.cuh"
 
 namespace ulc {
 
@@ -41,11 +42,15 @@ constexpr int kIdxSmem = 1024 + kIdxStages * kIdxStageBytes + kIdxQBytes + kIdxM
 // One query per request (decode): a short ring and small query tile, so that three CTAs share an
 // SM (3 x 74 KB of shared memory, 3 x 128 TMEM columns) and one CTA's prologue and ring fill
 // overlap the others' streaming.  More queries per request keep the deep ring, one CTA per SM.
-template <int NQ>
+// HIST: the epilogue also builds, per score row, the 2048-bin histogram the radix select starts
+// from (a shared-memory histogram per CTA, flushed to the select's workspace at the end), so that the
+// select kernel needs no pass of its own over the scores to find its threshold bin.
+template <int NQ, bool HIST = false>
 struct IdxGeom {
-  static constexpr int kStages = NQ == 1 ? 4 : kIdxStages;
+  static constexpr int kStages = NQ == 1 ? (HIST ? 3 : 4) : (HIST && NQ == 4 ? 6 : kIdxStages);
   static constexpr int kQBytes = NQ * 64 * 128;
-  static constexpr int kSmem = 1024 + kStages * kIdxStageBytes + kQBytes + NQ * 64 * 4 + kIdxBarrierBytes;
+  static constexpr int kHistBytes = HIST ? NQ * kTopkBins * 4 : 0;
+  static constexpr int kSmem = 1024 + kStages * kIdxStageBytes + kQBytes + NQ * 64 * 4 + kIdxBarrierBytes + kHistBytes;
   static constexpr int kCtasPerSm = NQ == 1 ? 3 : 1;
 };
 
@@ -56,6 +61,7 @@ struct IndexScoreParams {
   const int32_t* lengths;     // [R] context length in tokens
   const uint8_t* pool;        // this rank's index page pool (for the scales)
   float* logits;              // [R * n_q, max_pages * 64]
+  uint32_t* topk_ws;          // workspace of the histogram-first select (nullable): per row 2048 counts + counters
   int32_t* status;
   int R, n_q, max_pages, ranks, rank, pages_per_rank, pages_per_cta;
 };
@@ -83,19 +89,20 @@ __device__ __forceinline__ int local_valid_tokens(int length, int alloc_page, in
   return left <= 0 ? 0 : (left >= kPageTokens ? kPageTokens : static_cast<int>(left));
 }
 
-template <int NQ>
-__global__ void __launch_bounds__(kIdxThreads, IdxGeom<NQ>::kCtasPerSm)
+template <int NQ, bool HIST>
+__global__ void __launch_bounds__(kIdxThreads, IdxGeom<NQ, HIST>::kCtasPerSm)
 index_score_kernel(const __grid_constant__ CUtensorMap tmap_keys, const IndexScoreParams p) {
   constexpr int N = NQ * 64;
-  constexpr int kStages = IdxGeom<NQ>::kStages;
+  constexpr int kStages = IdxGeom<NQ, HIST>::kStages;
   constexpr uint32_t kCols = N * 2 <= 128 ? 128 : N * 2 <= 256 ? 256 : 512;
   extern __shared__ uint8_t idx_smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(idx_smem_raw) + 1023) &
                                              ~static_cast<uintptr_t>(1023));
   uint8_t* sk = smem;
   uint8_t* sq = smem + kStages * kIdxStageBytes;
-  float* sw = reinterpret_cast<float*>(sq + IdxGeom<NQ>::kQBytes);
+  float* sw = reinterpret_cast<float*>(sq + IdxGeom<NQ, HIST>::kQBytes);
   IdxBarriers& bar = *reinterpret_cast<IdxBarriers*>(sw + NQ * 64);
+  uint32_t* s_hist = reinterpret_cast<uint32_t*>(reinterpret_cast<uint8_t*>(&bar) + kIdxBarrierBytes);   // [NQ][2048] when HIST
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int r = blockIdx.y;
@@ -114,6 +121,18 @@ index_score_kernel(const __grid_constant__ CUtensorMap tmap_keys, const IndexSco
     ptx::prefetch_tmap(&tmap_keys);
   }
   if (warp == 1) { ptx::tmem_alloc<kCols>(&bar.tmem_base); ptx::tmem_relinquish(); }
+  if constexpr (HIST) {
+    for (int i = threadIdx.x; i < NQ * kTopkBins; i += kIdxThreads) s_hist[i] = 0;
+    // the select kernel scans the valid prefix of a row: columns of whole pages this rank holds plus
+    // its share of the last, partial stripe of pages
+    if (blockIdx.x == 0 && threadIdx.x < NQ) {
+      const int stripe = kPageTokens * p.ranks;
+      const int full = length / stripe, rem = length - full * stripe;
+      const int mine = min(max(rem - p.rank * kPageTokens, 0), kPageTokens);
+      const int n_valid = min(full * kPageTokens + mine, p.max_pages * kPageTokens);
+      p.topk_ws[static_cast<size_t>(r * NQ + threadIdx.x) * (kTopkWsRowBytes / 4) + kTopkWsCtr + 3] = static_cast<uint32_t>(n_valid);
+    }
+  }
   for (int i = threadIdx.x; i < kIdxTablePages && pg0 + i < pg1; i += kIdxThreads) bar.pages[i] = table[pg0 + i];
   auto page_of = [&](int a) -> int32_t { return a - pg0 < kIdxTablePages ? bar.pages[a - pg0] : table[a]; };
   // queries of this request -> shared memory, 128-byte swizzled rows (one row per head)
@@ -187,11 +206,13 @@ index_score_kernel(const __grid_constant__ CUtensorMap tmap_keys, const IndexSco
     const size_t row_stride = static_cast<size_t>(p.max_pages) * kPageTokens;
     // The key scale of this thread's token is fetched one tile ahead, so that its latency hides
     // behind the wait for the accumulator and the arithmetic of the tile before.
+    bool inside_next = false;                 // the token lies below the request's length (whatever its page holds)
     auto fetch_scale = [&](int tile, bool& valid_out) -> float {
       const int a = pg0 + 2 * tile + pg_in_tile;
       int32_t phys = (tile < ntiles && a < pg1) ? page_of(a) : -1;
       if (phys >= p.pages_per_rank) phys = -1;
-      valid_out = phys >= 0 && off < local_valid_tokens(length, a, p.ranks, p.rank);
+      inside_next = tile < ntiles && a < pg1 && off < local_valid_tokens(length, a, p.ranks, p.rank);
+      valid_out = phys >= 0 && inside_next;
       return valid_out
           ? reinterpret_cast<const float*>(p.pool + static_cast<size_t>(phys) * kIndexPageBytes + kIndexPageKeyBytes)[off]
           : 0.f;
@@ -201,6 +222,7 @@ index_score_kernel(const __grid_constant__ CUtensorMap tmap_keys, const IndexSco
     for (int i = 0; i < ntiles; ++i) {
       const int ab = i & 1;
       const bool valid = valid_next;
+      const bool inside = inside_next;
       const float kscale = kscale_next;
       kscale_next = fetch_scale(i + 1, valid_next);
       if (*abort_flag || !ptx::mbar_wait(&bar.acc_full[ab], (i >> 1) & 1)) {
@@ -226,13 +248,25 @@ index_score_kernel(const __grid_constant__ CUtensorMap tmap_keys, const IndexSco
           part[h & 3] = fmaf(sw[j * 64 + 32 + h], fmaxf(__uint_as_float(d1[h]), 0.f), part[h & 3]);
         }
         const float acc = (part[0] + part[1]) + (part[2] + part[3]);
+        const float logit = valid ? acc * kscale : -INFINITY;
         if (a < pg1)
-          p.logits[(static_cast<size_t>(r) * NQ + j) * row_stride + static_cast<size_t>(a) * kPageTokens + off] =
-              valid ? acc * kscale : -INFINITY;
+          p.logits[(static_cast<size_t>(r) * NQ + j) * row_stride + static_cast<size_t>(a) * kPageTokens + off] = logit;
+        if constexpr (HIST) {
+          if (inside) atomicAdd(&s_hist[j * kTopkBins + window_bin(order_key(logit))], 1u);
+        }
       }
       ptx::tc_fence_before();
       __syncwarp();
       if (lane == 0) ptx::mbar_arrive(&bar.acc_empty[ab]);
+    }
+    if constexpr (HIST) {
+      // the four epilogue warps flush this CTA's non-empty bins into the rows' histograms
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      const int et = threadIdx.x - 64;
+      for (int i = et; i < NQ * kTopkBins; i += 128) {
+        const uint32_t c = s_hist[i];
+        if (c) atomicAdd(p.topk_ws + static_cast<size_t>(r * NQ + i / kTopkBins) * (kTopkWsRowBytes / 4) + (i % kTopkBins), c);
+      }
     }
   }
   ptx::tc_fence_before();
@@ -291,12 +325,13 @@ __global__ void candidate_scatter_kernel(const float* __restrict__ vals, const i
   __threadfence_system();
 }
 
-template <int NQ>
+template <int NQ, bool HIST>
 static int launch_index_score(const CUtensorMap& tm, const IndexScoreParams& p, dim3 grid, cudaStream_t s) {
   static PerDeviceOnce once;
-  const int rc = ensure_dynamic_smem(reinterpret_cast<const void*>(index_score_kernel<NQ>), IdxGeom<NQ>::kSmem, once);
+  const int rc = ensure_dynamic_smem(reinterpret_cast<const void*>(index_score_kernel<NQ, HIST>),
+                                     IdxGeom<NQ, HIST>::kSmem, once);
   if (rc != 0) return rc;
-  index_score_kernel<NQ><<<grid, kIdxThreads, IdxGeom<NQ>::kSmem, s>>>(tm, p);
+  index_score_kernel<NQ, HIST><<<grid, kIdxThreads, IdxGeom<NQ, HIST>::kSmem, s>>>(tm, p);
   return static_cast<int>(cudaGetLastError());
 }
 
@@ -307,9 +342,24 @@ using namespace ulc;
 
 // q8 [R, n_q, 64, 128] fp8; w [R, n_q, 64] fp32; page_table [R, max_pages]; lengths [R];
 // pool: this rank's index pages (8448 bytes each); logits [R*n_q, max_pages*64] fp32.
+// topk_ws (nullable): workspace of ulc_topk_ws (ulc_topk_workspace_bytes(R * n_q) bytes, zero when first
+// used).  When given, the kernel also leaves every row's histogram and valid length there for
+// ulc_topk_ws(..., hist_ready = 1), and the columns beyond a request's pages are NOT filled with -inf
+// (the select kernel reads only the valid prefix).
+int ulc_index_score_hist(const void* q8, const float* w, const int32_t* page_table, const int32_t* lengths,
+                         const void* pool, int pages_per_rank, int R, int n_q, int max_pages, int ranks, int rank,
+                         int pages_per_cta, float* logits, void* topk_ws, int32_t* status, cudaStream_t stream);
+
 int ulc_index_score(const void* q8, const float* w, const int32_t* page_table, const int32_t* lengths,
                     const void* pool, int pages_per_rank, int R, int n_q, int max_pages, int ranks, int rank,
                     int pages_per_cta, float* logits, int32_t* status, cudaStream_t stream) {
+  return ulc_index_score_hist(q8, w, page_table, lengths, pool, pages_per_rank, R, n_q, max_pages, ranks, rank,
+                              pages_per_cta, logits, nullptr, status, stream);
+}
+
+int ulc_index_score_hist(const void* q8, const float* w, const int32_t* page_table, const int32_t* lengths,
+                         const void* pool, int pages_per_rank, int R, int n_q, int max_pages, int ranks, int rank,
+                         int pages_per_cta, float* logits, void* topk_ws, int32_t* status, cudaStream_t stream) {
   if (R <= 0 || max_pages <= 0) return 0;
   if (n_q < 1 || n_q > kIdxMaxQueries || n_q == 3) return -kErrUnsupported;
   if (reinterpret_cast<uintptr_t>(pool) & 127) return -kErrAlignment;
@@ -319,6 +369,7 @@ int ulc_index_score(const void* q8, const float* w, const int32_t* page_table, c
   IndexScoreParams p;
   p.q8 = reinterpret_cast<const uint8_t*>(q8); p.w = w; p.page_table = page_table; p.lengths = lengths;
   p.pool = reinterpret_cast<const uint8_t*>(pool); p.logits = logits; p.status = status;
+  p.topk_ws = reinterpret_cast<uint32_t*>(topk_ws);
   p.R = R; p.n_q = n_q; p.max_pages = max_pages; p.ranks = ranks; p.rank = rank;
   p.pages_per_rank = pages_per_rank;
   if (pages_per_cta <= 0) {
@@ -332,11 +383,18 @@ int ulc_index_score(const void* q8, const float* w, const int32_t* page_table, c
   }
   p.pages_per_cta = pages_per_cta + (pages_per_cta & 1);
   dim3 grid((max_pages + p.pages_per_cta - 1) / p.pages_per_cta, R);
+  if (topk_ws != nullptr) {
+    switch (n_q) {
+      case 1: return launch_index_score<1, true>(tm, p, grid, stream);
+      case 2: return launch_index_score<2, true>(tm, p, grid, stream);
+      default: return launch_index_score<4, true>(tm, p, grid, stream);
+    }
+  }
   index_fill_tail_kernel<<<dim3(8, R), 256, 0, stream>>>(p);
   switch (n_q) {
-    case 1: rc = launch_index_score<1>(tm, p, grid, stream); break;
-    case 2: rc = launch_index_score<2>(tm, p, grid, stream); break;
-    default: rc = launch_index_score<4>(tm, p, grid, stream); break;
+    case 1: rc = launch_index_score<1, false>(tm, p, grid, stream); break;
+    case 2: rc = launch_index_score<2, false>(tm, p, grid, stream); break;
+    default: rc = launch_index_score<4, false>(tm, p, grid, stream); break;
   }
   return rc;
 }

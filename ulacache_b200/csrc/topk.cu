@@ -43,12 +43,12 @@
 // :547).
 #include "ulc/launch.h"
 #include "ulc/ptx.cuh"
+#include "ulc/topk_key.cuh"
 
 namespace ulc {
 
 constexpr int kTopkThreads = 512;
 constexpr int kTopkWarps = kTopkThreads / 32;
-constexpr int kTopkBins = 2048;
 constexpr int kTopkCand = 2048;      // shared-memory candidate slots (elements of the threshold bin)
 constexpr int kTopkRankMax = 512;    // up to this many candidates are resolved by rank counting
 constexpr int kTopkMaxCluster = 8;
@@ -56,34 +56,6 @@ constexpr int kTopkFilters = 8;      // candidate cut-offs of the filter step
 constexpr uint64_t kNoKey = 1ull << 32;   // "above every key"
 // ranks of the sorted sample tried as cut-offs, relative to the expected one
 __constant__ float kTopkRankSpread[kTopkFilters] = {0.6f, 0.85f, 1.15f, 1.5f, 2.f, 3.f, 4.5f, 8.f};
-
-__device__ __forceinline__ uint32_t order_key(float x) {
-  uint32_t u = __float_as_uint(x);
-  if (x != x) u = 0xff800000u;   // NaN sorts as -inf
-  return (u & 0x80000000u) ? ~u : (u | 0x80000000u);
-}
-
-// Histogram bin of an order-preserving key: monotone (not strictly) in the key.
-__device__ __forceinline__ uint32_t window_bin(uint32_t key) {
-  const bool nonneg = (key & 0x80000000u) != 0u;
-  const uint32_t mag = (nonneg ? key : ~key) & 0x7fffffffu;        // exponent | mantissa of |x|
-  const int t = static_cast<int>(mag >> 18) - (112 << 5);           // exponent 112 = 2^-15
-  const uint32_t bp = static_cast<uint32_t>(min(max(t, 0), 1023));
-  return nonneg ? 1024u + bp : 1023u - bp;
-}
-
-// Smallest key of bin b (0 .. 2047).  Key 0 is reserved for "no element", so bin 0 starts at 1.
-__device__ __forceinline__ uint32_t bin_lo_key(uint32_t b) {
-  if (b == 0u) return 1u;
-  if (b >= 1024u) {
-    const uint32_t bp = b - 1024u;
-    return 0x80000000u | (bp == 0u ? 0u : ((bp + 3584u) << 18));
-  }
-  // negative scores: the smallest key of the bin belongs to its LARGEST magnitude
-  const uint32_t bp = 1023u - b;
-  const uint32_t mhi = bp == 1023u ? 0x7fffffffu : (((bp + 3585u) << 18) - 1u);
-  return 0x7fffffffu - mhi;
-}
 
 struct TopkShared {
   uint32_t hist[kTopkBins];      // this CTA's survivors (level 1, then level 2)
@@ -252,6 +224,95 @@ __device__ __forceinline__ uint32_t warp_inclusive_scan(uint32_t v) {
     if (lane >= static_cast<uint32_t>(o)) v += u;
   }
   return v;
+}
+
+// Step 4 of the selection, run by one CTA: `need` of the `in_bin` elements with key_cand <= key <
+// key_above are still to be selected.  They sit in s.cand_key / s.cand_pos (`parked`) or are
+// re-read from the row `x` of `n` elements.  Output slots are claimed from s.out_count.
+__device__ __forceinline__ void resolve_threshold_bin(TopkShared& s, const float* x, int n, bool parked, uint32_t in_bin,
+                                                      uint32_t need, uint32_t key_cand, uint64_t key_above,
+                                                      int32_t* oi, float* ov, int k, const TopkXform& xf) {
+  const int t = threadIdx.x;
+  const int cn = parked ? static_cast<int>(in_bin) : n;
+  auto in_range = [&](uint32_t key) { return key >= key_cand && static_cast<uint64_t>(key) < key_above; };
+  if (in_bin == need) {   // the whole threshold bin is selected
+    for (int jb = 0; jb < cn; jb += kTopkThreads) {
+      const int j = jb + t;
+      uint32_t key = 0; int32_t pos = 0;
+      bool take = j < cn;
+      if (take) {
+        if (parked) { key = s.cand_key[j]; pos = s.cand_pos[j]; }
+        else { key = order_key(x[j]); pos = j; take = in_range(key); }
+      }
+      const uint32_t at = claim_slots(&s.out_count, take);
+      if (at != 0xffffffffu) write_out(oi, ov, k, at, pos, key, xf);
+    }
+  } else if (parked && cn <= kTopkRankMax) {
+    // Few candidates: a candidate is selected iff fewer than `need` candidates beat it, where
+    // "beats" compares the score and then prefers the lower position.  G threads share a candidate.
+    int P = 16;
+    while (P < cn) P <<= 1;
+    const int G = kTopkThreads / P;              // 1 .. 32 consecutive lanes per candidate
+    const int j = t / G, g = t % G;
+    uint32_t key = 0; int32_t pos = 0;
+    uint32_t rank = 0;
+    if (j < cn) {
+      key = s.cand_key[j]; pos = s.cand_pos[j];
+      for (int i = g; i < cn; i += G) {
+        const uint32_t ki = s.cand_key[i];
+        const int32_t pi = s.cand_pos[i];
+        rank += (ki > key || (ki == key && pi < pos)) ? 1u : 0u;
+      }
+    }
+    for (int o = 1; o < G; o <<= 1) rank += __shfl_xor_sync(0xffffffffu, rank, o);
+    const bool take = j < cn && g == 0 && rank < need;
+    const uint32_t at = claim_slots(&s.out_count, take);
+    if (at != 0xffffffffu) write_out(oi, ov, k, at, pos, key, xf);
+  } else {
+    // Radix levels over the 64-bit composite (key, 0xffffffff - position), 11 bits a level,
+    // over the parked candidates or (a threshold range too crowded to park) over the row itself.
+    uint64_t prefix = 0, mask = 0;
+    bool done = false;
+    for (int shift = 53; !done; shift -= 11) {
+      const int sh = shift < 0 ? 0 : shift;
+      const uint32_t nb_mask = shift < 0 ? 0x1ffu : 0x7ffu;   // the last level has 9 bits
+      for (int i = t; i < kTopkBins; i += kTopkThreads) s.hist[i] = 0;
+      __syncthreads();
+      for (int j = t; j < cn; j += kTopkThreads) {
+        uint32_t key; int32_t pos;
+        if (parked) { key = s.cand_key[j]; pos = s.cand_pos[j]; }
+        else { key = order_key(x[j]); pos = j; if (!in_range(key)) continue; }
+        const uint64_t comp = (static_cast<uint64_t>(key) << 32) | (0xffffffffu - static_cast<uint32_t>(pos));
+        if ((comp & mask) == prefix) atomicAdd(&s.hist[(comp >> sh) & nb_mask], 1u);
+      }
+      __syncthreads();
+      find_threshold<kTopkBins>(s, s.hist, need);
+      const uint32_t d = s.thr_bin;
+      const uint32_t above = s.thr_above;
+      const uint32_t at_d = s.thr_count;
+      const bool last = (at_d == need - above) || shift < 0;
+      __syncthreads();
+      for (int jb = 0; jb < cn; jb += kTopkThreads) {
+        const int j = jb + t;
+        uint32_t key = 0; int32_t pos = 0;
+        bool take = false;
+        if (j < cn) {
+          if (parked) { key = s.cand_key[j]; pos = s.cand_pos[j]; take = true; }
+          else { key = order_key(x[j]); pos = j; take = in_range(key); }
+          const uint64_t comp = (static_cast<uint64_t>(key) << 32) | (0xffffffffu - static_cast<uint32_t>(pos));
+          const uint32_t dig = (comp >> sh) & nb_mask;
+          take = take && (comp & mask) == prefix && (dig > d || (last && dig == d));
+        }
+        const uint32_t at = claim_slots(&s.out_count, take);
+        if (at != 0xffffffffu) write_out(oi, ov, k, at, pos, key, xf);
+      }
+      prefix |= static_cast<uint64_t>(d) << sh;
+      mask |= static_cast<uint64_t>(nb_mask) << sh;
+      need -= above;
+      done = last;
+      __syncthreads();
+    }
+  }
 }
 
 struct TopkArgs {
@@ -549,89 +610,171 @@ topk_select_kernel(const TopkArgs a, const int cap) {
   TOPK_T(7);
 
   // ---- step 4: resolve the threshold bin (CTA 0) ---------------------------------------------------
-  const int cn = parked ? static_cast<int>(in_bin) : n;
-  auto in_range = [&](uint32_t key) { return key >= key_cand && static_cast<uint64_t>(key) < key_above; };
-  if (in_bin == need) {   // the whole threshold bin is selected
-    for (int jb = 0; jb < cn; jb += kTopkThreads) {
-      const int j = jb + t;
-      uint32_t key = 0; int32_t pos = 0;
-      bool take = j < cn;
-      if (take) {
-        if (parked) { key = s.cand_key[j]; pos = s.cand_pos[j]; }
-        else { key = order_key(x[j]); pos = j; take = in_range(key); }
-      }
-      const uint32_t at = claim_slots(&s.out_count, take);
-      if (at != 0xffffffffu) write_out(oi, ov, k, at, pos, key, xf);
-    }
-  } else if (parked && cn <= kTopkRankMax) {
-    // Few candidates: a candidate is selected iff fewer than `need` candidates beat it, where
-    // "beats" compares the score and then prefers the lower position.  G threads share a candidate.
-    int P = 16;
-    while (P < cn) P <<= 1;
-    const int G = kTopkThreads / P;              // 1 .. 32 consecutive lanes per candidate
-    const int j = t / G, g = t % G;
-    uint32_t key = 0; int32_t pos = 0;
-    uint32_t rank = 0;
-    if (j < cn) {
-      key = s.cand_key[j]; pos = s.cand_pos[j];
-      for (int i = g; i < cn; i += G) {
-        const uint32_t ki = s.cand_key[i];
-        const int32_t pi = s.cand_pos[i];
-        rank += (ki > key || (ki == key && pi < pos)) ? 1u : 0u;
-      }
-    }
-    for (int o = 1; o < G; o <<= 1) rank += __shfl_xor_sync(0xffffffffu, rank, o);
-    const bool take = j < cn && g == 0 && rank < need;
-    const uint32_t at = claim_slots(&s.out_count, take);
-    if (at != 0xffffffffu) write_out(oi, ov, k, at, pos, key, xf);
-  } else {
-    // Radix levels over the 64-bit composite (key, 0xffffffff - position), 11 bits a level,
-    // over the parked candidates or (a threshold range too crowded to park) over the row itself.
-    uint64_t prefix = 0, mask = 0;
-    bool done = false;
-    for (int shift = 53; !done; shift -= 11) {
-      const int sh = shift < 0 ? 0 : shift;
-      const uint32_t nb_mask = shift < 0 ? 0x1ffu : 0x7ffu;   // the last level has 9 bits
-      for (int i = t; i < kTopkBins; i += kTopkThreads) s.hist[i] = 0;
-      __syncthreads();
-      for (int j = t; j < cn; j += kTopkThreads) {
-        uint32_t key; int32_t pos;
-        if (parked) { key = s.cand_key[j]; pos = s.cand_pos[j]; }
-        else { key = order_key(x[j]); pos = j; if (!in_range(key)) continue; }
-        const uint64_t comp = (static_cast<uint64_t>(key) << 32) | (0xffffffffu - static_cast<uint32_t>(pos));
-        if ((comp & mask) == prefix) atomicAdd(&s.hist[(comp >> sh) & nb_mask], 1u);
-      }
-      __syncthreads();
-      find_threshold<kTopkBins>(s, s.hist, need);
-      const uint32_t d = s.thr_bin;
-      const uint32_t above = s.thr_above;
-      const uint32_t at_d = s.thr_count;
-      const bool last = (at_d == need - above) || shift < 0;
-      __syncthreads();
-      for (int jb = 0; jb < cn; jb += kTopkThreads) {
-        const int j = jb + t;
-        uint32_t key = 0; int32_t pos = 0;
-        bool take = false;
-        if (j < cn) {
-          if (parked) { key = s.cand_key[j]; pos = s.cand_pos[j]; take = true; }
-          else { key = order_key(x[j]); pos = j; take = in_range(key); }
-          const uint64_t comp = (static_cast<uint64_t>(key) << 32) | (0xffffffffu - static_cast<uint32_t>(pos));
-          const uint32_t dig = (comp >> sh) & nb_mask;
-          take = take && (comp & mask) == prefix && (dig > d || (last && dig == d));
-        }
-        const uint32_t at = claim_slots(&s.out_count, take);
-        if (at != 0xffffffffu) write_out(oi, ov, k, at, pos, key, xf);
-      }
-      prefix |= static_cast<uint64_t>(d) << sh;
-      mask |= static_cast<uint64_t>(nb_mask) << sh;
-      need -= above;
-      done = last;
-      __syncthreads();
-    }
-  }
+  resolve_threshold_bin(s, x, n, parked, in_bin, need, key_cand, key_above, oi, ov, k, xf);
   __syncthreads();
   TOPK_T(8);
   if (t == 0 && a.out_count) a.out_count[row] = min(static_cast<uint32_t>(k), s.out_count);
+}
+
+
+// ---- selection from a row histogram that already exists in global memory ------------------------
+//
+// When the histogram of a row is built somewhere else - by `topk_hist_kernel` below, or by the
+// index-score kernel in its epilogue, which sees every score anyway - selection needs no
+// communication between the CTAs that share a row: each reads the 2048 counts, finds the threshold
+// bin itself, and claims output slots per warp from a counter in global memory.  The last CTA of a
+// row to finish (a ticket) resolves the threshold bin and puts the workspace back to zero, so the
+// next launch can use it as it is.
+//
+// Workspace (device memory, zero when first used), per row:
+//   [0, 8192)        uint32 hist[2048]
+//   [8192, 8208)     uint32 emitted, parked, ticket, valid row length (written by the histogram's producer)
+//   [8448, 16640)    uint32 cand_key[2048]
+//   [16640, 24832)   int32  cand_pos[2048]
+struct TopkWsArgs {
+  TopkArgs a;
+  uint32_t* ws;
+  int splits;          // CTAs per row
+  int len_from_ws;     // row length = ws counter 3 (set by the producer of the histogram) instead of lengths / max_len
+};
+
+__global__ void __launch_bounds__(kTopkThreads)
+topk_hist_kernel(const TopkWsArgs w) {
+  __shared__ uint32_t hist[kTopkBins];
+  const int row = blockIdx.y, t = threadIdx.x;
+  const TopkArgs& a = w.a;
+  const float* x = a.scores + static_cast<size_t>(row) * a.row_stride;
+  const int n = a.lengths ? min(max(a.lengths[row], 0), a.max_len) : a.max_len;
+  if (n <= a.k) return;                  // the select kernel copies such a row; it reads no histogram
+  for (int i = t; i < kTopkBins; i += kTopkThreads) hist[i] = 0;
+  __syncthreads();
+  for (uint32_t i = blockIdx.x * kTopkThreads + t; i < static_cast<uint32_t>(n); i += gridDim.x * kTopkThreads)
+    atomicAdd(&hist[window_bin(order_key(__ldg(x + i)))], 1u);
+  __syncthreads();
+  uint32_t* g = w.ws + static_cast<size_t>(row) * (kTopkWsRowBytes / 4);
+  for (int b = t; b < kTopkBins; b += kTopkThreads) {
+    const uint32_t c = hist[b];
+    if (c) atomicAdd(g + b, c);
+  }
+}
+
+__global__ void __launch_bounds__(kTopkThreads, 2)
+topk_select_from_hist_kernel(const TopkWsArgs w) {
+  __shared__ TopkShared s;
+  __shared__ int s_last;
+  const TopkArgs& a = w.a;
+  const int row = blockIdx.y, t = threadIdx.x;
+  const uint32_t lane = t & 31;
+  const uint32_t S = gridDim.x, part = blockIdx.x;
+  uint32_t* g = w.ws + static_cast<size_t>(row) * (kTopkWsRowBytes / 4);
+  uint32_t* ctr = g + kTopkWsCtr;
+  const float* x = a.scores + static_cast<size_t>(row) * a.row_stride;
+  TopkXform xf;
+  xf.in_idx = a.in_idx ? a.in_idx + static_cast<size_t>(row) * a.in_idx_stride : nullptr;
+  xf.table = a.xform ? a.xform + static_cast<size_t>(row) * a.xform_stride : nullptr;
+  xf.pages = a.pages ? a.pages + static_cast<size_t>(row / a.rows_per_request) * a.pages_stride : nullptr;
+  xf.ranks = a.ranks; xf.rank = a.rank; xf.drop_neg_inf = a.drop_neg_inf;
+  const int k = a.k;
+  int32_t* oi = a.out_idx + static_cast<size_t>(row) * k;
+  float* ov = a.out_val ? a.out_val + static_cast<size_t>(row) * k : nullptr;
+  int n = a.max_len;
+  if (w.len_from_ws) n = min(static_cast<int>(__ldcg(ctr + 3)), a.max_len);
+  else if (a.lengths) n = min(max(a.lengths[row], 0), a.max_len);
+
+  if (n <= k) {
+    // short row: everything is selected.  A producer that builds histograms does so for every row,
+    // so the row's workspace still goes back to zero.
+    if (part == 0) {
+      for (int i = t; i < k; i += kTopkThreads) {
+        oi[i] = i < n ? xform_value(xf, i, x[i]) : -1;
+        if (ov) ov[i] = i < n ? x[i] : -INFINITY;
+      }
+      if (t == 0 && a.out_count) a.out_count[row] = n;
+      if (w.len_from_ws) {
+        for (int i = t; i < kTopkBins; i += kTopkThreads) g[i] = 0;
+        if (t < 4) ctr[t] = 0;
+      }
+    }
+    return;
+  }
+
+  find_threshold<kTopkBins>(s, g, static_cast<uint32_t>(k));
+  const uint32_t b1 = s.thr_bin;
+  const uint32_t need = static_cast<uint32_t>(k) - s.thr_above;
+  const uint32_t in_bin = s.thr_count;
+  const uint32_t key_cand = bin_lo_key(b1);
+  const uint64_t key_above = b1 < 2047u ? bin_lo_key(b1 + 1u) : kNoKey;
+  const bool parked = in_bin <= static_cast<uint32_t>(kTopkCand);
+
+  // this CTA's blocks of the row: part, part + S, ...; eight loads per thread are in flight at once,
+  // and a row short enough for one such round (the usual case) is read from memory once
+  const uint32_t un = static_cast<uint32_t>(n);
+  const uint32_t stride = S * kTopkThreads;
+  const uint32_t first = part * kTopkThreads + t;
+  const bool single = first + 8u * stride >= un || stride * 8u >= un;
+  uint32_t keys[8];
+  auto load8 = [&](uint32_t base) {
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const uint32_t i = base + j * stride;
+      keys[j] = i < un ? order_key(__ldg(x + i)) : 0u;
+    }
+  };
+  uint32_t na = 0, nc = 0;
+  for (uint32_t base = first; base < un; base += 8u * stride) {
+    load8(base);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const bool above = static_cast<uint64_t>(keys[j]) >= key_above;
+      na += above ? 1u : 0u;
+      nc += (!above && keys[j] >= key_cand) ? 1u : 0u;
+    }
+  }
+  if (!parked) nc = 0;
+  const uint32_t ia = warp_inclusive_scan(na), ic = warp_inclusive_scan(nc);
+  uint32_t wa = 0, wc = 0;
+  if (lane == 31) {                                   // one claim per warp, straight from the row's counters
+    wa = ia ? atomicAdd(ctr + 0, ia) : 0u;
+    wc = ic ? atomicAdd(ctr + 1, ic) : 0u;
+  }
+  uint32_t pa = __shfl_sync(0xffffffffu, wa, 31) + ia - na;
+  uint32_t pc = __shfl_sync(0xffffffffu, wc, 31) + ic - nc;
+  for (uint32_t base = first; base < un; base += 8u * stride) {
+    if (!single) load8(base);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const uint32_t key = keys[j];
+      const uint32_t i = base + j * stride;
+      if (static_cast<uint64_t>(key) >= key_above) {
+        write_out(oi, ov, k, pa++, static_cast<int32_t>(i), key, xf);
+      } else if (parked && key >= key_cand) {
+        if (pc < static_cast<uint32_t>(kTopkCand)) {
+          g[kTopkWsKey + pc] = key;
+          g[kTopkWsPos + pc] = i;
+        }
+        ++pc;
+      }
+    }
+  }
+  // ticket: the last CTA of the row to get here finishes it
+  __threadfence();
+  __syncthreads();
+  if (t == 0) s_last = atomicAdd(ctr + 2, 1u) == S - 1 ? 1 : 0;
+  __syncthreads();
+  if (!s_last) return;
+  __threadfence();
+  if (t == 0) s.out_count = __ldcg(ctr + 0);
+  if (parked)
+    for (uint32_t i = t; i < in_bin; i += kTopkThreads) {
+      s.cand_key[i] = __ldcg(g + kTopkWsKey + i);
+      s.cand_pos[i] = static_cast<int32_t>(__ldcg(g + kTopkWsPos + i));
+    }
+  __syncthreads();
+  resolve_threshold_bin(s, x, n, parked, in_bin, need, key_cand, key_above, oi, ov, k, xf);
+  __syncthreads();
+  if (t == 0 && a.out_count) a.out_count[row] = min(static_cast<uint32_t>(k), s.out_count);
+  for (int i = t; i < kTopkBins; i += kTopkThreads) g[i] = 0;      // leave the workspace as it was found
+  if (t < 4) ctr[t] = 0;
 }
 
 template <int CS>
@@ -709,6 +852,43 @@ int ulc_topk_ex(const float* scores, long long row_stride, const int32_t* length
     case 4: return launch_topk<4>(a, rows, static_cast<int>(cap), stream);
     default: return launch_topk<8>(a, rows, static_cast<int>(cap), stream);
   }
+}
+
+
+// Bytes of workspace `ulc_topk_ws` needs for `rows` rows.  The memory must be zero the first time it
+// is used; every call leaves it zero again.  Calls that share a workspace must not overlap on the GPU.
+long long ulc_topk_workspace_bytes(int rows) { return static_cast<long long>(rows) * ulc::kTopkWsRowBytes; }
+
+// As ulc_topk_ex, in two launches without clusters: a histogram kernel, then a selection kernel in
+// which the CTAs of a row do not communicate (see topk_select_from_hist_kernel).
+//   hist_ready = 1: the row histograms are already in the workspace (built by ulc_index_score with
+//   its `topk_ws` argument) together with every row's valid length; `lengths` is then ignored.
+int ulc_topk_ws(const float* scores, long long row_stride, const int32_t* lengths, int rows, int max_len,
+                int k, const int32_t* in_idx, long long in_idx_stride, const int32_t* xform,
+                long long xform_stride, const int32_t* pages, long long pages_stride, int rows_per_request,
+                int ranks, int rank, int drop_neg_inf, int32_t* out_idx, float* out_val, int32_t* out_count,
+                void* workspace, int hist_ready, cudaStream_t stream) {
+  using namespace ulc;
+  if (rows <= 0) return 0;
+  if (k <= 0 || k > 2048 || max_len < 0 || workspace == nullptr) return -kErrUnsupported;
+  if (rows_per_request < 1) rows_per_request = 1;
+  TopkWsArgs w;
+  TopkArgs& a = w.a;
+  a.scores = scores; a.row_stride = row_stride; a.lengths = lengths; a.max_len = max_len; a.k = k;
+  a.in_idx = in_idx; a.in_idx_stride = in_idx_stride; a.xform = xform; a.xform_stride = xform_stride;
+  a.pages = pages; a.pages_stride = pages_stride; a.rows_per_request = rows_per_request;
+  a.ranks = ranks; a.rank = rank; a.drop_neg_inf = drop_neg_inf;
+  a.out_idx = out_idx; a.out_val = out_val; a.out_count = out_count;
+  w.ws = reinterpret_cast<uint32_t*>(workspace);
+  w.len_from_ws = hist_ready ? 1 : 0;
+  // eight elements per thread, but no more CTAs than fill the machine a few times over
+  long long per_row = (static_cast<long long>(max_len) + kTopkThreads * 8 - 1) / (kTopkThreads * 8);
+  while (per_row > 1 && per_row * rows > 8 * 148) per_row = (per_row + 1) / 2;
+  w.splits = static_cast<int>(per_row < 1 ? 1 : per_row);
+  const dim3 grid(static_cast<unsigned>(w.splits), static_cast<unsigned>(rows));
+  if (!hist_ready) topk_hist_kernel<<<grid, kTopkThreads, 0, stream>>>(w);
+  topk_select_from_hist_kernel<<<grid, kTopkThreads, 0, stream>>>(w);
+  return static_cast<int>(cudaGetLastError());
 }
 
 #ifdef ULC_TOPK_TRACE

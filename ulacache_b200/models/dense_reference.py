@@ -190,10 +190,10 @@ class DenseReferenceDecoder:
             p = torch.softmax(scores * c.softmax_scale, dim=-1)
             out[b] = torch.einsum("hs,hsd->hd", p, v).reshape(-1)
         self._last_index = chosen
-        oq = _fake_quant_act(_bf16(out))
+        oq = _fake_quant_act(out)
         return _bf16(oq @ d["w_o"].t())
 
-    def _ffn(self, d: dict, h, hq):
+    def _ffn(self, d: dict, h, hq, pinned_choice=None):
         import torch
 
         c = self.cfg
@@ -205,6 +205,9 @@ class DenseReferenceDecoder:
         logits = _bf16(h @ d["router"].t())
         sc = torch.sigmoid(logits)
         choice = torch.topk(sc + d["router_bias"], c.experts_per_token, dim=-1).indices
+        self.routing.append((sc, choice))
+        if pinned_choice is not None:           # random-init routers score all experts nearly alike: near-ties
+            choice = pinned_choice.long()       # are the rule, so the experts can be pinned to the kernels' choice
         g = torch.gather(sc, 1, choice)
         g = g / g.sum(-1, keepdim=True) * c.routed_scale
         out = torch.zeros_like(h)
@@ -224,7 +227,7 @@ class DenseReferenceDecoder:
             out[b] = acc
         return _bf16(out)
 
-    def step(self, tokens, positions, selections=None):
+    def step(self, tokens, positions, selections=None, routing=None):
         """One decode step: ``tokens`` [B] at ``positions`` [B] (tokens already in each request's
         cache).  ``selections[layer][b]``: optional record positions to attend to (to pin the oracle
         to the very selection the kernels made); by default the oracle takes its own top-k.
@@ -234,6 +237,9 @@ class DenseReferenceDecoder:
         c = self.cfg
         x = self.embed[tokens.long()].clone()                  # bf16-valued residual stream
         delta = None
+        self.sublayers = []                                    # (attention output, feed-forward output) per layer
+        self.routing = []                                      # (expert scores, own choice) per MoE layer
+        moe_seen = 0
         for l, d in enumerate(self.layers):
             if delta is not None:
                 x = _bf16(x + delta)
@@ -241,7 +247,12 @@ class DenseReferenceDecoder:
             attn = self._attention(l, d, _fake_quant_act(h), positions, selections)
             x = _bf16(x + attn)
             h2 = _rms(x, d["ffn_norm"], c.rms_eps)
-            delta = self._ffn(d, h2, _fake_quant_act(h2))
+            pin = None
+            if routing is not None and not d["dense"]:
+                pin = routing[moe_seen][0]
+                moe_seen += 1
+            delta = self._ffn(d, h2, _fake_quant_act(h2), pin)
+            self.sublayers.append((attn, delta))
         x = _bf16(x + delta)
         hf = _fake_quant_act(_rms(x, self.final_norm, c.rms_eps))
         return _bf16(hf @ self.lm_head.t())[:, : c.vocab]

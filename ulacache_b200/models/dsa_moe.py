@@ -139,7 +139,7 @@ class _Fp8Linear:
         if peer_out is not None:
             if self.pad != self.nout:
                 raise ValueError("peer outputs need an unpadded output width")
-            return fp8.grouped_gemm(x8, sx, self.q, self.s, splits=1, status=status, max_rows=x8.shape[0],
+            return fp8.grouped_gemm(x8, sx, self.q, self.s, splits=self.splits, status=status, max_rows=x8.shape[0],
                                     peer_out=peer_out)
         y = fp8.grouped_gemm(x8, sx, self.q, self.s, splits=self.splits, status=status,
                              max_rows=min(self.rows_hint or x8.shape[0], x8.shape[0]))
@@ -269,6 +269,9 @@ class DsaMoeModel:
 
         self.deterministic = (_os.environ.get("ULC_DETERMINISTIC", "0") == "1") if deterministic is None else deterministic
         self.shared_placement = _os.environ.get("ULC_MOE_SHARED_PLACEMENT", "0") == "1"
+        # W_UV product with the o_proj input quantiser in its epilogue: one launch fewer, but measured
+        # slower than the two kernels at 32 rows (two TMEM passes in the epilogue), so off by default
+        self._fused_oquant = _os.environ.get("ULC_FUSED_OQUANT", "0") == "1"
         self._sm_count = torch.cuda.get_device_properties(self.device).multi_processor_count if self.device.type == "cuda" else 0
         hint = _os.environ.get("ULC_DENSE_ROWS_HINT", "")
         if hint:
@@ -321,7 +324,16 @@ class DsaMoeModel:
                                                 rank=rank, gen=gen, shard_gen=shard_gen, dense_tp=1 if self.dpa else tp,
                                                 q_replicated=self.owner_attention))
         self._ag_by_rows = {}
+        # The index-score kernel leaves each row's score histogram in this workspace and the radix
+        # select starts from it (ULC_TOPK_FUSED=0: separate score and select kernels, for comparison).
+        self._topk_ws = None
+        if self.device.type == "cuda" and _os.environ.get("ULC_TOPK_FUSED", "1") == "1":
+            from ..ops import topk as _topk
+
+            self._topk_ws = _topk.workspace(max_batch, self.device)
         self.record_selections = None       # a list here makes every layer append its selected record IDs
+        self.record_sublayers = None        # ... and (attention output, feed-forward output) of every layer
+        self.record_routing = None          # ... and (expert choice, gate) of every MoE layer
         self.last_logits = None
         if self.deterministic:
             # split-K sums partial products with fp32 atomics, in an order that varies from run to run
@@ -493,7 +505,7 @@ class DsaMoeModel:
         self._mark("index.score")
         logits = indexer.index_score(iq8, iwf, batch.req_pages, self._ctx, self.index_pool[layer],
                                      ranks=self.kv_ranks, rank=self.rank if self.mode == "tp" else 0,
-                                     status=self.status)
+                                     status=self.status, topk_workspace=self._topk_ws)
         self._mark("index.topk")
         sel = self._select(logits, batch)
         if self.deterministic:
@@ -522,10 +534,15 @@ class DsaMoeModel:
                 status=self.status)
         self.cache.finish_layer_attention(layer)
         self._mark("attn.absorb gemm")
-        o = torch.empty((B, out_heads * c.v_dim), dtype=torch.bfloat16, device=qb.device)
-        gemm.batched_linear(o_lat, w.w_uv_t, o.view(B, out_heads, c.v_dim))
+        # o[b, h, :] = o_lat[b, h, :] @ W_UV[h]; each head's 128 values are one fp8 group of the o_proj
+        # input, so the product leaves its kernel quantised
+        if self._fused_oquant:
+            o8, os_ = gemm.batched_linear_quant(o_lat, w.w_uv_t, status=self.status)
+        else:                                   # separate product and quantiser (ULC_FUSED_OQUANT=0, for comparison)
+            o = torch.empty((B, out_heads * c.v_dim), dtype=torch.bfloat16, device=qb.device)
+            gemm.batched_linear(o_lat, w.w_uv_t, o.view(B, out_heads, c.v_dim))
+            o8, os_ = fp8.act_quant(o)
         self._mark("attn.w_o gemm")
-        o8, os_ = fp8.act_quant(o)
         if self.attn_tp > 1 and self.ar is not None:
             w.w_o(o8, os_, self.status, peer_out=self._peer_targets())      # scatter phase in the GEMM epilogue
             self._mark("comm")
@@ -540,7 +557,7 @@ class DsaMoeModel:
 
         c = self.cfg
         if self.kv_ranks == 1:
-            return indexer.select_topk(logits, c.topk, batch.req_pages, n_q=1)
+            return indexer.select_topk(logits, c.topk, batch.req_pages, n_q=1, hist_workspace=self._topk_ws)
         return self._distributed_select(logits, batch)
 
     def _distributed_select(self, logits, batch: DecodeBatch):
@@ -552,7 +569,7 @@ class DsaMoeModel:
 
         c = self.cfg
         ids, vals = indexer.select_topk(logits, c.topk, batch.req_pages, n_q=1, ranks=self.kv_ranks, rank=self.rank,
-                                        with_values=True)
+                                        with_values=True, hist_workspace=self._topk_ws)
         if self.cand is not None:
             cand_v, cand_i = self.cand.exchange(ids, vals)
             return topk_op.topk(cand_v, c.topk, in_idx=cand_i)
@@ -590,6 +607,8 @@ class DsaMoeModel:
         # one split when bit-reproducible steps are asked for)
         logits = gemm.linear(h, w.router, splits=1 if self.deterministic else 0, status=self.status)
         choice, gate = glue.moe_topk(logits, w.router_bias, c.experts_per_token, c.routed_scale)
+        if self.record_routing is not None:             # (eager runs only: for oracles)
+            self.record_routing.append((choice.clone(), gate.clone()))
         b_local = B
         if self.dpa:
             # every rank's experts see every rank's tokens: gather activations and routing decisions
@@ -660,7 +679,10 @@ class DsaMoeModel:
         self._mark("norm+quant")
         h, h8, hs = glue.add_rmsnorm_quant(x, attn[0], w.ffn_norm, c.rms_eps, want_h=not w.dense,
                                            n_slots=attn[1], slot_stride=attn[2])
-        return self._ffn(w, h, h8, hs)
+        out = self._ffn(w, h, h8, hs)
+        if self.record_sublayers is not None:           # (eager single-rank runs only: for oracles)
+            self.record_sublayers.append((attn[0].clone(), out[0].clone()))
+        return out
 
     def _head(self, x, delta, n_rows):
         """Final norm, sharded lm_head, greedy sample -> int32 [n_rows] (this rank's rows)."""

@@ -129,8 +129,31 @@ def grouped_gemm_reference(x8, sx, w8, sw, offs=None):
     return out
 
 
+_SPLITK_WS = {}
+SPLITK_WS_BYTES = 24 << 20
+
+
+def splitk_workspace(device):
+    """Per-device scratch of the in-kernel split-K reduction (partial tiles + tickets), zero when
+    created; every GEMM leaves it ready for the next.  GEMMs that use it must be ordered on one
+    stream.  Create it (one GEMM call, or this function) before capturing a CUDA graph."""
+    import torch
+
+    device = torch.device(device)
+    key = device.index if device.index is not None else torch.cuda.current_device()
+    if key not in _SPLITK_WS:
+        _SPLITK_WS[key] = torch.zeros(SPLITK_WS_BYTES, dtype=torch.uint8, device=device)
+    return _SPLITK_WS[key]
+
+
+def _splitk_fits(m, nout, splits, max_rows):
+    if 0 < max_rows < m:          # several passes over the rows: the partial tiles of one pass would be overwritten
+        return False
+    return m <= 32 and nout // 128 <= 1024 and 4096 + (nout // 128) * splits * 32 * 128 * 4 <= SPLITK_WS_BYTES
+
+
 def grouped_gemm(x8, sx, w8, sw, offs=None, *, splits=1, out=None, status=None, work=None, max_rows=0,
-                 peer_out=None, active=None):
+                 peer_out=None, active=None, peer_rows=0):
     """``y[m] = x[m] @ w[expert(m)]^T`` with block scales.  ``w8`` is TILE-MAJOR
     ([E,] Nout/128, K/128, 128, 128; see ``tile_weight``); ``offs`` int32 [E+1] gives each
     expert's row range (rows sorted by expert); ``max_rows`` bounds the rows of one expert
@@ -148,8 +171,21 @@ def grouped_gemm(x8, sx, w8, sw, offs=None, *, splits=1, out=None, status=None, 
     e, nout, k = w8.shape[0], w8.shape[1] * 128, w8.shape[2] * 128
     m = x8.shape[0]
     assert x8.is_contiguous() and w8.is_contiguous() and sx.is_contiguous() and sw.is_contiguous()
+    if splits > 1 and e == 1 and _splitk_fits(m, nout, splits, max_rows):
+        # dense layer at decode size: K splits reduced inside the kernel (no cleared fp32 buffer, no
+        # atomics, no conversion launch); the result may also go straight to peers
+        ws = splitk_workspace(x8.device)
+        if out is None and not peer_out:
+            out = torch.empty((m, nout), dtype=torch.bfloat16, device=x8.device)
+        n = len(peer_out) if peer_out else 0
+        arr = (C.c_void_p * max(n, 1))(*(peer_out or [0]))
+        N.check(N.cuda().ulc_fp8_gemm_splitk(
+            N.ptr(x8), N.ptr(sx), N.ptr(w8), N.ptr(sw), C.c_int(m), C.c_int(nout), C.c_int(k), C.c_int(splits),
+            C.c_int(max_rows), N.ptr(out), arr, C.c_int(n), C.c_int(peer_rows), N.ptr(ws), C.c_longlong(ws.numel()),
+            N.ptr(status), N.stream()), "fp8_grouped_gemm")
+        return out
     if peer_out:
-        assert splits == 1
+        splits = 1
         if e > 1 and work is None:
             work = torch.empty(e + 1, dtype=torch.int32, device=x8.device)
         arr = (C.c_void_p * len(peer_out))(*peer_out)
@@ -199,7 +235,10 @@ def pick_splits(nout: int, k: int, experts: int = 1, sm_count: int = 148) -> int
         per = (kb + s - 1) // s
         items = tiles * ((kb + per - 1) // per)
         rounds = (items + sm_count - 1) // sm_count
-        cost = rounds * (per * 16384 / 44000.0 + 1.5) + (3.0 if s > 1 else 0.0)      # microseconds
+        # microseconds: a K block streams in 0.37 us at one SM's share of the HBM bandwidth; an item
+        # costs about 4 us of pipeline fill and epilogue drain; the in-kernel reduction reads one more
+        # partial tile per split (measured on the decode projections at 32 rows)
+        cost = rounds * (per * 16384 / 44000.0 + 4.0) + (0.5 * s if s > 1 else 0.0)
         if best_cost is None or cost < best_cost - 1e-9:
             best, best_cost = s, cost
     return best

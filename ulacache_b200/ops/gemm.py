@@ -58,3 +58,28 @@ def batched_linear(x, w, out):
         C.c_longlong(N_ * K), C.c_longlong(out.stride(1)), C.c_int(1), C.c_void_p(0), C.c_void_p(0), N.stream())
     N.check(code, "gemm_wt_bf16")
     return out
+
+
+def batched_linear_quant(x, w, *, status=None):
+    """``batched_linear`` whose result leaves the kernel already quantised for the next fp8 GEMM:
+    returns (uint8 fp8 [T, batch * N], fp32 scales [T, batch * N / 128]) with one scale per token
+    and 128 output features (``N`` a multiple of 128).  On the CPU: the reference product followed
+    by the reference quantiser."""
+    import torch
+    from . import fp8
+
+    T, Bt, K = x.shape
+    N_ = w.shape[1]
+    assert N_ % 128 == 0 and w.shape[0] == Bt and w.shape[2] == K
+    if not x.is_cuda:
+        y = torch.einsum("tbk,bnk->tbn", x.float(), w.float()).reshape(T, Bt * N_)
+        return fp8.act_quant_reference(y)
+    assert x.stride(2) == 1 and w.is_contiguous()
+    q = torch.empty((T, Bt * N_), dtype=torch.uint8, device=x.device)
+    sc = torch.empty((T, Bt * N_ // 128), dtype=torch.float32, device=x.device)
+    code = N.cuda().ulc_gemm_wt_bf16_batched_quant(
+        N.ptr(x), N.ptr(w), N.ptr(q), N.ptr(sc), C.c_int(T), C.c_int(N_), C.c_int(K), C.c_longlong(x.stride(0)),
+        C.c_longlong(K), C.c_longlong(Bt * N_), C.c_longlong(Bt * N_ // 128), C.c_int(Bt), C.c_longlong(x.stride(1)),
+        C.c_longlong(N_ * K), C.c_longlong(N_), N.ptr(status), N.stream())
+    N.check(code, "gemm_wt_bf16_quant")
+    return q, sc

@@ -51,9 +51,13 @@ def index_score_reference(q8, w, page_table, lengths, pool, *, ranks=1, rank=0):
     return out
 
 
-def index_score(q8, w, page_table, lengths, pool, *, ranks=1, rank=0, pages_per_cta=0, out=None, status=None):
+def index_score(q8, w, page_table, lengths, pool, *, ranks=1, rank=0, pages_per_cta=0, out=None, status=None,
+                topk_workspace=None):
     """Score this rank's index shard.  ``pool`` uint8 [pages, 8448]; returns fp32
-    ``[R*n_q, max_pages*64]`` (column = allocation page * 64 + offset)."""
+    ``[R*n_q, max_pages*64]`` (column = allocation page * 64 + offset).  ``topk_workspace``
+    (``ops.topk.workspace(R * n_q, device)``): the kernel also leaves every row's histogram and
+    valid length there for ``select_topk(..., hist_workspace=...)``; columns beyond a request's
+    pages are then left unwritten."""
     import torch
 
     R, n_q = q8.shape[0], q8.shape[1]
@@ -62,10 +66,10 @@ def index_score(q8, w, page_table, lengths, pool, *, ranks=1, rank=0, pages_per_
         return index_score_reference(q8, w, page_table, lengths, pool, ranks=ranks, rank=rank)
     if out is None:
         out = torch.empty((R * n_q, max_pages * 64), dtype=torch.float32, device=q8.device)
-    code = N.cuda().ulc_index_score(
+    code = N.cuda().ulc_index_score_hist(
         N.ptr(q8), N.ptr(w), N.ptr(page_table), N.ptr(lengths), N.ptr(pool), C.c_int(pool.shape[0]),
         C.c_int(R), C.c_int(n_q), C.c_int(max_pages), C.c_int(ranks), C.c_int(rank), C.c_int(pages_per_cta),
-        N.ptr(out), N.ptr(status), N.stream())
+        N.ptr(out), N.ptr(topk_workspace), N.ptr(status), N.stream())
     N.check(code, "index_score")
     return out
 
@@ -89,13 +93,15 @@ def cols_to_ids(cols, page_table, *, n_q, ranks, rank, out=None):
     return out
 
 
-def select_topk(logits, k, page_table, *, n_q, ranks=1, rank=0, with_values=False):
-    """Local top-k of the score rows, translated to logical IDs (-1 where nothing valid)."""
+def select_topk(logits, k, page_table, *, n_q, ranks=1, rank=0, with_values=False, hist_workspace=None):
+    """Local top-k of the score rows, translated to logical IDs (-1 where nothing valid).
+    ``hist_workspace``: see ``ops.topk.topk_paged_ids``."""
     import torch
 
     if logits.is_cuda:
         vals = torch.empty((logits.shape[0], k), dtype=torch.float32, device=logits.device) if with_values else None
-        ids = topk_op.topk_paged_ids(logits, k, page_table, rows_per_request=n_q, ranks=ranks, rank=rank, out_val=vals)
+        ids = topk_op.topk_paged_ids(logits, k, page_table, rows_per_request=n_q, ranks=ranks, rank=rank, out_val=vals,
+                                     hist_workspace=hist_workspace)
         return (ids, vals) if with_values else ids
     cols = topk_op.topk_reference(logits, k)
     vals = torch.gather(logits, 1, cols.clamp(min=0).long())

@@ -51,7 +51,8 @@ def init_distributed():
 class DecodeEngine:
     def __init__(self, cfg, *, batch: int, prompt_len: int, max_new_tokens: int, mode: str = "tp",
                  rank: int = 0, world: int = 1, local_rank: int = 0, group=None, cpu_group=None,
-                 host_record_capacity: int = 0, use_graph: bool = True, seed: int = 0,
+                 host_record_capacity: int = 0, device_record_capacity: Optional[int] = None,
+                 use_graph: bool = True, seed: int = 0,
                  kv_transport: str = "auto", comm: str = "peer", spec_steps: int = 3, force_accept=None,
                  tp_attention: str = "owner"):
         import torch
@@ -75,8 +76,14 @@ class DecodeEngine:
         total = (prompt_len + max_new_tokens * rows_per_request + rows_per_request + span - 1) // span * span
         pages = total // span
         # every owner holds total / kv_ranks tokens of every request
-        slots = batch * total // kv_ranks + 64
-        slots = (slots + 63) // 64 * 64
+        needed = (batch * total // kv_ranks + 64 + 63) // 64 * 64
+        # With a host tier the records of a rank are split between HBM slots and pinned host slots
+        # (``device_record_capacity`` + ``host_record_capacity`` must hold all of them); promotions and
+        # evictions then run inside every decode step.
+        slots = needed if device_record_capacity is None else (int(device_record_capacity) + 63) // 64 * 64
+        if slots + host_record_capacity < needed:
+            raise ValueError(f"{needed} records per rank are needed, the tiers hold {slots} + {host_record_capacity}")
+        self.records_needed = needed
         self.geometry = EngineGeometry(batch, total, pages, slots, batch * pages + 2)
         self.prompt_len, self.max_new_tokens = prompt_len, max_new_tokens
         plane = record_plane(cfg.kv_format)
@@ -232,6 +239,7 @@ class DecodeEngine:
 
         inv = self.cache.memory_inventory()
         return {"weights_bytes": self.model.weight_bytes(), "kv_bytes": inv["device_key_value_bytes"],
+                "host_kv_bytes": inv["host_key_value_bytes"], "host_records_per_rank": inv["host_record_capacity"],
                 "kv_metadata_bytes": inv["metadata_bytes"], "index_bytes": self.index_pool.numel(),
                 "allocated_bytes": torch.cuda.memory_allocated(self.device),
                 "kv_records_per_rank": inv["device_record_capacity"]}
