@@ -310,7 +310,9 @@ class CacheEngine:
                 if self._storage_of_layer[l] != a:
                     self._layer_events[l] = done
 
-    def _resolve(self, g: int, layer: int, sel):
+    def _resolve(self, g: int, layer: int, sel, *, merge: bool = True):
+        """Physical locations of ``sel``.  ``merge=False`` (collective transports): only what this
+        rank owns, -1 elsewhere; the caller combines the owners' answers itself."""
         import torch
 
         res = self.residency[g]
@@ -324,7 +326,8 @@ class CacheEngine:
                 # peers' directories are not addressable: keep only what this rank owns, then merge
                 owner = (sel >> self.owners.stripe_shift) % self.owners.ranks
                 loc = torch.where((sel > 0) & (owner == self.my_rank), loc, torch.full_like(loc, -1))
-                loc = self.transport.merge_locations(loc)
+                if merge:
+                    loc = self.transport.merge_locations(loc)
             return loc
         ids = sel.to(torch.int32)
         mine, local = res._owned_locals(ids.reshape(-1))
@@ -334,7 +337,7 @@ class CacheEngine:
         vals = torch.where(ok, (self.my_rank << 28) | e, torch.full_like(e, -1))
         loc[mine] = vals
         loc = loc.view(sel.shape)
-        if self.transport is not None and self.owners.ranks > 1:
+        if merge and self.transport is not None and self.owners.ranks > 1:
             loc = self.transport.merge_locations(loc)
         return loc
 

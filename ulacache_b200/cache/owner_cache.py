@@ -42,6 +42,7 @@ class RecordOwnerPagedResidency(CacheEngine):
                          replicated_selections=bindings.native_selections_replicated)
         self.world = world
         self.writes_replicated = bindings.native_record_writes_replicated
+        self._loc_all = {}          # group -> every consumer's resolved locations (collective transports)
 
     def _check_agreement(self, spec, bindings):
         """Every owner must have been configured identically; disagreement is a start-up error."""
@@ -82,10 +83,36 @@ class RecordOwnerPagedResidency(CacheEngine):
         self._exchange_group(g, layer)
         res.commit()
         self.transport.barrier()
-        loc = self._resolve(g, layer, sel)
+        if self.transport.kind == "collective":
+            # Peers' directories are not addressable: every owner resolves EVERY consumer's selection
+            # for the records it owns, an element-wise max combines the owners' answers, and each
+            # consumer keeps its own slice (all of it stays around for the record gather below).
+            k = a.maximum_selected_record_count
+            owned = self._resolve(g, layer, union[:, :, :k].contiguous(), merge=False)
+            everyone_loc = self.transport.merge_locations(owned)
+            self._loc_all[g] = everyone_loc
+            loc = everyone_loc[self.my_rank, :sel.shape[0], :sel.shape[1]].contiguous()
+        else:
+            loc = self._resolve(g, layer, sel)
         self._loc[g] = loc
         self._sel[g] = sel
         return loc
+
+    def gather_window(self, layer: int):
+        """Independent selections over a collective transport: owners contribute the rows of every
+        consumer's selection, a sum assembles them, each consumer keeps its own window."""
+        import torch
+
+        g = self.groups.group(layer)
+        if (self.world == 1 or self.replicated_selections or self.transport.kind != "collective"
+                or g not in self._loc_all):
+            return super().gather_window(layer)
+        everyone = self._loc_all[g]
+        window = self.transport.gather_window(self, layer, everyone)
+        q, k = self._sel[g].shape
+        per = everyone.shape[1] * everyone.shape[2]
+        mine = window[self.my_rank * per:(self.my_rank + 1) * per].view(everyone.shape[1], everyone.shape[2], -1)
+        return mine[:q, :k].reshape(q * k, -1).contiguous()
 
     def write(self, layer, ids, values, *, owner_only=None):
         """Replicated writers: only the owner stores.  Independent writers on a symmetric
