@@ -75,12 +75,15 @@ def test_decode_step_matches_dense_reference(native, monkeypatch, prompt):
         err = (got - want).abs().max().item()
         scale = want.abs().max().item()
         worst = max(worst, err / scale)
-        assert err <= 0.08 * scale + 1e-3, (step, err, scale)
+        rms = ((got - want).norm() / want.norm()).item()
+        # worst element within 12 % of the largest logit and the whole matrix within 10 % relative rms
+        # (the noise measured across accumulation orders is 4 to 9 % and 4 to 7 %)
+        assert err <= 0.12 * scale + 1e-3 and rms <= 0.10, (step, err, scale, rms)
         # greedy tokens agree unless the oracle's two best logits are within the tolerance
         top2 = torch.topk(want, 2, dim=-1).values
         gap = (top2[:, 0] - top2[:, 1])
         same = eng.batch.out_tokens.long() == want.argmax(dim=-1)
-        assert bool((same | (gap <= 0.08 * scale)).all()), (step, eng.batch.out_tokens.tolist(), want.argmax(-1).tolist())
+        assert bool((same | (gap <= 0.12 * scale)).all()), (step, eng.batch.out_tokens.tolist(), want.argmax(-1).tolist())
         mismatched += int((~same).sum())
     assert mismatched <= steps * B // 4, mismatched        # (a tiny random-init model has many near-tied logits)
     eng.close()

@@ -21,4 +21,4 @@ def test_two_rank_peer_protocols():
     assert res.returncode == 0, res.stdout[-2000:] + res.stderr[-4000:]
     line = [l for l in res.stdout.splitlines() if l.startswith("{")][-1]
     out = json.loads(line)
-    assert out["all_ranks_ok"] and all(out.values()), out
+    assert out["all_ranks_ok"] and all(v for k, v in out.items() if not k.endswith("_error")), out

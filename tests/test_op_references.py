@@ -36,8 +36,11 @@ def test_topk_reference_lengths_ties_and_tables():
 
 
 def test_pick_splits_prefers_full_rounds():
-    # 56 feature tiles x 128 K blocks (o_proj): 5 splits give 280 items = two rounds of 148 CTAs
-    assert fp8.pick_splits(7168, 16384) == 5
+    # 56 feature tiles x 128 K blocks (o_proj): 2 splits = 112 items in ONE round of 148 CTAs; the
+    # per-item cost makes this beat 5 splits (280 items, two rounds), as measured at 32 rows
+    assert fp8.pick_splits(7168, 16384) == 2
+    # 18 feature tiles (the fused input projection): split until one round is nearly full
+    assert fp8.pick_splits(2304, 7168) * 18 <= 148
     # enough tiles for every SM: no split
     assert fp8.pick_splits(32768, 1536) == 1
     assert 1 <= fp8.pick_splits(2304, 7168) <= 16

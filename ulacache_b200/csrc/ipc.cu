@@ -110,6 +110,20 @@ int ulc_ipc_open_handle(const unsigned char* handle64, void** out_base) {
   return 0;
 }
 
+// Unmap ONE peer allocation opened with ulc_ipc_open_handle (by the base address it returned).
+// A process may hold several symmetric heaps at once; closing one must leave the others mapped.
+int ulc_ipc_close_handle(void* base) {
+  std::lock_guard<std::mutex> lock(g_ipc_mutex);
+  for (auto it = g_open_handles.begin(); it != g_open_handles.end(); ++it) {
+    if (it->second == base) {
+      const cudaError_t e = cudaIpcCloseMemHandle(base);
+      g_open_handles.erase(it);
+      return static_cast<int>(e);
+    }
+  }
+  return 0;      // not (or no longer) mapped: nothing to do
+}
+
 int ulc_ipc_close_all() {
   std::lock_guard<std::mutex> lock(g_ipc_mutex);
   int rc = 0;

@@ -212,6 +212,65 @@ class _LayerWeights:
                 self.s13 = _Fp8Linear(2 * sf, c.hidden, device, shard_gen)
                 self.s2 = _Fp8Linear(c.hidden, sf, device, shard_gen)
 
+    def shard_(self, cfg: DsaMoeConfig, *, tp: int, rank: int, attn_tp: int, dense_tp: int, q_replicated: bool):
+        """Turn FULL (one-rank) weights into this rank's shard in place, so that an N-rank model and a
+        one-rank model built from the same random stream are the same network (validation runs on
+        small configurations; the full-size model draws each rank's shard directly)."""
+        import torch
+
+        c = cfg
+
+        def rows(lin, lo, hi):                    # keep output rows [lo, hi) (multiples of 128)
+            lin.q = lin.q[lo // 128: hi // 128].contiguous()
+            lin.s = lin.s[lo // 128: hi // 128].contiguous()
+            lin.nout = lin.pad = hi - lo
+
+        def cols(lin, lo, hi):                    # keep input columns [lo, hi) (multiples of 128)
+            lin.q = lin.q[:, lo // 128: hi // 128].contiguous()
+            lin.s = lin.s[:, lo // 128: hi // 128].contiguous()
+            lin.k = hi - lo
+
+        if attn_tp > 1:
+            heads = c.heads // attn_tp
+            h0 = rank * heads
+            if not q_replicated:
+                per = c.nope_dim + c.rope_dim
+                keep = torch.cat([self.w_qb.q[h0 * per // 128:(h0 + heads) * per // 128],
+                                  self.w_qb.q[c.heads * per // 128:]])
+                keep_s = torch.cat([self.w_qb.s[h0 * per // 128:(h0 + heads) * per // 128],
+                                    self.w_qb.s[c.heads * per // 128:]])
+                self.w_qb.q, self.w_qb.s = keep.contiguous(), keep_s.contiguous()
+                self.qb_splits = (heads * per, c.index_heads * c.index_dim)
+                self.w_qb.nout = self.w_qb.pad = sum(self.qb_splits)
+                self.w_uk_t = self.w_uk_t[h0:h0 + heads].contiguous()
+            self.w_uv_t = self.w_uv_t[h0:h0 + heads].contiguous()
+            cols(self.w_o, h0 * c.v_dim, (h0 + heads) * c.v_dim)
+        from ..ops import fp8
+
+        for lin in (self.w_qb, self.w_o):
+            lin.splits = fp8.pick_splits(lin.pad, lin.k)
+        if self.dense:
+            if dense_tp > 1:
+                ffn = c.dense_ffn // dense_tp
+                f0 = rank * ffn
+                q, sc = self.w13.q, self.w13.s
+                self.w13.q = torch.cat([q[f0 // 128:(f0 + ffn) // 128],
+                                        q[(c.dense_ffn + f0) // 128:(c.dense_ffn + f0 + ffn) // 128]]).contiguous()
+                self.w13.s = torch.cat([sc[f0 // 128:(f0 + ffn) // 128],
+                                        sc[(c.dense_ffn + f0) // 128:(c.dense_ffn + f0 + ffn) // 128]]).contiguous()
+                self.w13.nout = self.w13.pad = 2 * ffn
+                cols(self.w2, f0, f0 + ffn)
+                for lin in (self.w13, self.w2):
+                    lin.splits = fp8.pick_splits(lin.pad, lin.k)
+        elif tp > 1:
+            local = c.experts // tp
+            lo = rank * local
+            pick = list(range(lo, lo + local)) + ([c.experts] if self.shared_fused else [])
+            idx = torch.tensor(pick, device=self.e13_q.device)
+            self.e13_q, self.e13_s = self.e13_q[idx].contiguous(), self.e13_s[idx].contiguous()
+            self.e2_q, self.e2_s = self.e2_q[idx].contiguous(), self.e2_s[idx].contiguous()
+            self.local_experts, self.expert_lo = local, lo
+
     def nbytes(self) -> int:
         import torch
 
@@ -252,7 +311,7 @@ class DsaMoeModel:
     def __init__(self, cfg: DsaMoeConfig, *, device, cache, index_pool, tp: int = 1, rank: int = 0,
                  group=None, cpu_group=None, mode: str = "tp", max_batch: int = 64, max_context: int = 65536,
                  seed: int = 0, comm: str = "peer", deterministic: Optional[bool] = None,
-                 tp_attention: str = "owner"):
+                 tp_attention: str = "owner", weights_from_full: bool = False):
         import torch
         from ..ops import _native as N
         from ..ops import records
@@ -292,15 +351,32 @@ class DsaMoeModel:
         self.status = N.new_status(self.device)
         unique = cfg.unique_layer_weights or cfg.layers
         self._unique = []
+        self.weights_from_full = weights_from_full
         for l in range(min(unique, cfg.layers)):
             # unique set l is dense when l < dense_layers; MoE layers cycle over the MoE sets
+            if weights_from_full:
+                # (validation) the one-rank network from the common stream, cut down to this rank's shard
+                w = _LayerWeights(cfg, l, device=self.device, attn_tp=1, tp=1, rank=0, gen=gen, shard_gen=gen, dense_tp=1)
+                w.shard_(cfg, tp=tp, rank=rank, attn_tp=self.attn_tp, dense_tp=1 if self.dpa else tp,
+                         q_replicated=self.owner_attention)
+                self._unique.append(w)
+                continue
             self._unique.append(_LayerWeights(cfg, l, device=self.device, attn_tp=self.attn_tp, tp=tp, rank=rank,
                                               gen=gen, shard_gen=shard_gen, dense_tp=1 if self.dpa else tp,
                                               q_replicated=self.owner_attention))
         self.embed = (torch.randn(cfg.vocab, cfg.hidden, device=self.device, generator=gen) * 0.02).to(torch.bfloat16)
         self.final_norm = torch.ones(cfg.hidden, dtype=torch.bfloat16, device=self.device)
         self.vocab_local = (cfg.vocab + tp - 1) // tp
-        self.lm_head = _Fp8Linear(self.vocab_local, cfg.hidden, self.device, shard_gen)
+        if weights_from_full and tp > 1:
+            if cfg.vocab % (128 * tp):
+                raise ValueError("weights_from_full needs a vocabulary that splits into 128-row tiles per rank")
+            full = _Fp8Linear(cfg.vocab, cfg.hidden, self.device, gen)
+            full.q = full.q[rank * self.vocab_local // 128:(rank + 1) * self.vocab_local // 128].contiguous()
+            full.s = full.s[rank * self.vocab_local // 128:(rank + 1) * self.vocab_local // 128].contiguous()
+            full.nout = full.pad = self.vocab_local
+            self.lm_head = full
+        else:
+            self.lm_head = _Fp8Linear(self.vocab_local, cfg.hidden, self.device, gen if weights_from_full else shard_gen)
         # rotary tables
         half = cfg.rope_dim // 2
         inv = 1.0 / (cfg.rope_theta ** (torch.arange(0, half, device=self.device).float() / half))
@@ -334,6 +410,9 @@ class DsaMoeModel:
         self.record_selections = None       # a list here makes every layer append its selected record IDs
         self.record_sublayers = None        # ... and (attention output, feed-forward output) of every layer
         self.record_routing = None          # ... and (expert choice, gate) of every MoE layer
+        self.force_routing = None           # a list of (choice, gate) here replaces the router's decision, one
+        #                                     entry per MoE layer in order (eager runs only: two layouts of one
+        #                                     network compared without near-tied experts flipping between them)
         self.last_logits = None
         if self.deterministic:
             # split-K sums partial products with fp32 atomics, in an order that varies from run to run
@@ -607,6 +686,8 @@ class DsaMoeModel:
         # one split when bit-reproducible steps are asked for)
         logits = gemm.linear(h, w.router, splits=1 if self.deterministic else 0, status=self.status)
         choice, gate = glue.moe_topk(logits, w.router_bias, c.experts_per_token, c.routed_scale)
+        if self.force_routing is not None:
+            choice, gate = self.force_routing.pop(0)
         if self.record_routing is not None:             # (eager runs only: for oracles)
             self.record_routing.append((choice.clone(), gate.clone()))
         b_local = B

@@ -42,6 +42,8 @@ class SymmetricHeap:
         self._native = None
         self.base = 0
         self.peer_bases = [0] * world_size
+        self.peer_devices = [0] * world_size
+        self._opened = []
         self._flag_epoch = 0
         if self.device.type != "cuda":
             self._host = torch.zeros(self.nbytes, dtype=torch.uint8)
@@ -75,16 +77,19 @@ class SymmetricHeap:
         offset = C.c_ulonglong()
         N.check(N.cuda().ulc_ipc_get_handle(C.c_void_p(self.base), handle, C.byref(offset)), "ipc_get_handle")
         mine = (socket.gethostname(), bytes(handle), int(offset.value))
+        mine = mine + (int(self.device.index or 0),)
         gathered = [None] * self.world
         dist.all_gather_object(gathered, mine, group=self.cpu_group)
         if len({g[0] for g in gathered}) != 1:
             raise RuntimeError("All ranks of a symmetric heap must run on one host")
-        for r, (_, h, off) in enumerate(gathered):
+        self.peer_devices = [g[3] for g in gathered]          # CUDA device ordinal of every rank
+        for r, (_, h, off, _dev) in enumerate(gathered):
             if r == self.rank:
                 continue
             out = C.c_void_p()
             buf = (C.c_ubyte * 64).from_buffer_copy(h)
             N.check(N.cuda().ulc_ipc_open_handle(buf, C.byref(out)), f"ipc_open_handle(rank {r})")
+            self._opened.append(out.value)                    # mappings this heap must close itself
             self.peer_bases[r] = out.value + off
         dist.barrier(group=self.cpu_group)
 
@@ -141,7 +146,9 @@ class SymmetricHeap:
             if peer == self.rank:
                 continue
             flag = C.c_int()
-            N.check(N.cuda().ulc_p2p_native_atomics(C.c_int(self.device.index or 0), C.c_int(peer), C.byref(flag)),
+            # ranks are not device ordinals: ask about the device the peer rank actually runs on
+            N.check(N.cuda().ulc_p2p_native_atomics(C.c_int(self.device.index or 0),
+                                                    C.c_int(self.peer_devices[peer]), C.byref(flag)),
                     "p2p_native_atomics")
             ok = ok and bool(flag.value)
         return ok
@@ -155,7 +162,9 @@ class SymmetricHeap:
 
                 torch.cuda.synchronize()
                 dist.barrier(group=self.cpu_group)   # nobody frees while a peer may still read
-            self._native.cuda().ulc_ipc_close_all()
+            for base in self._opened:                         # only this heap's mappings: others stay usable
+                self._native.cuda().ulc_ipc_close_handle(C.c_void_p(base))
+            self._opened = []
             self._view = None
             self._native.cuda().ulc_slab_free(C.c_void_p(self.base))
             self.base = 0

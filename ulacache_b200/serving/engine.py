@@ -54,7 +54,7 @@ class DecodeEngine:
                  host_record_capacity: int = 0, device_record_capacity: Optional[int] = None,
                  use_graph: bool = True, seed: int = 0,
                  kv_transport: str = "auto", comm: str = "peer", spec_steps: int = 3, force_accept=None,
-                 tp_attention: str = "owner"):
+                 tp_attention: str = "owner", weights_from_full: bool = False):
         import torch
         from .. import client
         from ..bindings import LocalCacheBindings, TensorParallelCacheBindings
@@ -103,7 +103,8 @@ class DecodeEngine:
         self.index_pool = torch.zeros((cfg.cache_layers, self.geometry.index_pages, 8448), dtype=torch.uint8, device=self.device)
         self.model = DsaMoeModel(cfg, device=self.device, cache=self.cache, index_pool=self.index_pool, tp=world,
                                  rank=rank, group=group, cpu_group=cpu_group, mode=mode, max_batch=batch * rows_per_request,
-                                 max_context=total + 8, seed=seed, comm=comm, tp_attention=tp_attention)
+                                 max_context=total + 8, seed=seed, comm=comm, tp_attention=tp_attention,
+                                 weights_from_full=weights_from_full)
         i32 = dict(dtype=torch.int32, device=self.device)
         self.batch = DecodeBatch(tokens=torch.zeros(batch, **i32), lengths=torch.zeros(batch, **i32),
                                  req_pages=torch.full((batch, pages), -1, **i32), out_tokens=torch.zeros(batch, **i32))
@@ -246,4 +247,9 @@ class DecodeEngine:
 
     def close(self):
         self.graph = None
+        # the model's communication heap first (its peers' mappings are its own), then the cache's
+        heap = getattr(self.model, "comm_heap", None)
+        if heap is not None:
+            heap.close()
+            self.model.comm_heap = None
         self.cache.close()
