@@ -45,6 +45,24 @@ def main():
         dist.all_gather_into_tensor(ref, local_scores, group=group)
         ok = ok and bool(torch.equal(got, ref))
     out["tagged_all_gather"] = ok
+    # line all-gather with ragged rows, more calls than slots
+    from ..flashag import LineScoreAllGather
+
+    lg = LineScoreAllGather(heap, 9, 300, slots=2)
+    ok = True
+    for it in range(7):
+        local_scores = torch.randn(9, 300, device=dev) + rank * 10 + it
+        lens = torch.randint(0, 301, (9,), device=dev, dtype=torch.int32)
+        got, got_len = lg.all_gather(local_scores, lens if it % 3 else None, fill=-5.0)
+        if it % 3 == 0:
+            lens = torch.full((9,), 300, device=dev, dtype=torch.int32)
+        masked = torch.where(torch.arange(300, device=dev)[None, :] < lens[:, None], local_scores, torch.full_like(local_scores, -5.0))
+        ref = torch.empty((world, 9, 300), device=dev)
+        ref_len = torch.empty((world, 9), device=dev, dtype=torch.int32)
+        dist.all_gather_into_tensor(ref, masked, group=group)
+        dist.all_gather_into_tensor(ref_len, lens, group=group)
+        ok = ok and bool(torch.equal(got, ref)) and bool(torch.equal(got_len, ref_len))
+    out["line_all_gather_ragged"] = ok
     # reader lifetime
     pub = DistributedResidencyPublication(heap, domains=2)
     pub.publish(1, SELECTIONS_READY)
@@ -62,6 +80,41 @@ def main():
     ref_i = torch.empty((world, 4, 64), dtype=torch.int32, device=dev)
     dist.all_gather_into_tensor(ref_i, ids, group=group)
     out["candidate_exchange"] = bool(torch.equal(ci.view(4, world, 64), ref_i.permute(1, 0, 2)))
+    # owner-side Index scoring for independent queries: peer-memory protocol == the collective-composed one
+    from ..indexer.native_owner import PeerOwnerIndexScorer
+    from ..indexer.plan import IndexScorePlan
+    from ..indexer.scorer import OwnerIndexScorer
+    from ..ops import indexer as idx_ops, records
+    from ..storage import layout as L
+
+    rows, n_q, k, max_len = 4, 1, 128, 64 * world * 12
+    plan = IndexScorePlan(rows=rows, max_length=max_len, topk=k, ranks=world)
+    g = torch.Generator(device=dev).manual_seed(100 + rank)
+    pool_pages = 256
+    keys = torch.randn(pool_pages * 64, 128, device=dev, generator=g)
+    kq, ksc = records.encode_index_key(keys)
+    pool = torch.zeros(pool_pages, L.INDEX_PAGE_BYTES, dtype=torch.uint8, device=dev)
+    pool[:, :8192] = kq.view(pool_pages, 8192)
+    pool[:, 8192:] = ksc.view(pool_pages, 64).contiguous().view(torch.uint8).view(pool_pages, 256)
+    q8, wf = idx_ops.quantize_queries(torch.randn(rows, n_q, 64, 128, device=dev, generator=g),
+                                      torch.rand(rows, n_q, 64, device=dev, generator=g))
+    pages = plan.local_columns // 64
+    table = torch.stack([torch.stack([torch.randperm(pool_pages, device=dev, generator=g)[:pages] for _ in range(rows)])
+                         for _ in range(world)]).to(torch.int32)
+    lengths = torch.randint(max_len // 3, max_len + 1, (rows,), device=dev, generator=g, dtype=torch.int32)
+    lengths[0] = max_len
+    peer_scorer = PeerOwnerIndexScorer(heap, plan, n_q=n_q)
+    coll_scorer = OwnerIndexScorer(plan, rank=rank, group=group)
+    ok = True
+    for it in range(3):                       # both parities and a reuse
+        got = peer_scorer.score(q8, wf, table, lengths, pool, status=heap.status)
+        want = coll_scorer.score(q8, wf, table, lengths, pool, status=heap.status)
+        for r in range(rows * n_q):
+            a = set(t for t in got[r].tolist() if t >= 0)
+            b = set(t for t in want[r].tolist() if t >= 0)
+            ok = ok and len(a) == len(b) == min(k, int(lengths[r // n_q])) and len(a & b) >= 0.99 * len(b)
+        lengths = torch.clamp(lengths - 37, min=1)
+    out["owner_index_peer_protocol"] = ok
     torch.cuda.synchronize()
     N.raise_on_status(heap.status, "peer protocols")
     heap.close()

@@ -215,6 +215,19 @@ __device__ __forceinline__ int32_t ld_relaxed_sys(const int32_t* p) {
 __device__ __forceinline__ void st_relaxed_sys(int32_t* p, int32_t v) {
   asm volatile("st.relaxed.sys.global.b32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
+__device__ __forceinline__ uint32_t ld_relaxed_sys_u32(const uint32_t* p) {
+  uint32_t v;
+  asm volatile("ld.relaxed.sys.global.b32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ void st_relaxed_sys_v2(uint2* p, uint2 v) {      // one 8-byte store
+  asm volatile("st.relaxed.sys.global.v2.b32 [%0], {%1,%2};" ::"l"(p), "r"(v.x), "r"(v.y) : "memory");
+}
+__device__ __forceinline__ void st_relaxed_sys_v4(uint4* p, uint4 v) {      // one 16-byte store
+  asm volatile("st.relaxed.sys.global.v4.b32 [%0], {%1,%2,%3,%4};" ::"l"(p), "r"(v.x), "r"(v.y), "r"(v.z),
+               "r"(v.w)
+               : "memory");
+}
 // Wait until *flag >= want.  Gives up after `limit_cycles` and returns false.
 __device__ __forceinline__ bool wait_flag_ge(const int32_t* flag, int32_t want,
                                              long long limit_cycles) {
