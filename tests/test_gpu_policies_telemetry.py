@@ -75,3 +75,38 @@ def test_observers(native):
     rec.record(3, 2, sel[:20].cuda())              # 10240 triples: dropped whole
     assert rec.dropped == 20 * 512 and rec.drain() == 512
     assert rec.chunks[0][:, 2].tolist() == sel[0].tolist() and set(rec.chunks[0][:, 0]) == {3}
+
+
+def test_replay_probes_and_miss_trace_match_the_host_path(native):
+    """Device counters of the replay probes and the local-miss trace == their CPU twins on random inputs."""
+    from ulacache_b200.telemetry import DeviceReplayProbes, GpuTpMissTrace
+
+    g = torch.Generator().manual_seed(11)
+    dir_len, queries, width, topk = 4096, 24, 2, 64
+    directory = torch.randint(-40, 400, (dir_len,), generator=g, dtype=torch.int32)
+    directory[directory == -1] = -2                     # no unallocated rows: the snapshot must pass
+    selected = torch.randint(-1, dir_len, (queries, topk), generator=g, dtype=torch.int32)
+    selected[:, 5] = selected[:, 4]                     # duplicates inside a query
+    selected[1] = selected[0]                           # and across the two queries of a request
+    current = torch.randint(0, dir_len, (queries,), generator=g, dtype=torch.int32)
+    requests = torch.arange(queries // width, dtype=torch.int32) + 3
+    plan = torch.randint(-1, 50, (5, 128), generator=g, dtype=torch.int32)
+    count = torch.tensor([77], dtype=torch.int32)
+    outs = []
+    for dev in ("cpu", "cuda"):
+        p = DeviceReplayProbes(2, queries, topk, device=dev)
+        p.before_plan(1, selected.to(dev), current.to(dev), requests.to(dev), directory.to(dev), width=width)
+        p.after_group(1, plan.to(dev), count.to(dev), current.to(dev), directory.to(dev), layers=3, row_bytes=656)
+        outs.append(p.snapshot())
+    assert outs[0] == outs[1] and outs[0]["totals"]["lookup_tokens"] > 0
+    rows = torch.randint(0, 1000, (6, 16), generator=g, dtype=torch.int32)
+    counts = torch.randint(0, 17, (6,), generator=g, dtype=torch.int32)
+    snaps = []
+    for dev in ("cpu", "cuda"):
+        tr = GpuTpMissTrace(groups=3, query_rows=8, topk=16, frames=100, chunk_frames=4, device=dev)
+        for frame, valid in ((5, 6), (6, 3)):
+            tr.begin_frame(frame, valid)
+            tr.observe(frame % 3, rows.to(dev), counts.to(dev))
+        snaps.append(tr.snapshot_chunk())
+    for key in snaps[0]:
+        assert torch.equal(snaps[0][key], snaps[1][key]), key

@@ -134,7 +134,8 @@ def main():
     from ..serving.engine import DecodeEngine
 
     os.environ["ULC_DETERMINISTIC"] = "1"
-    cfg = DsaMoeConfig().tiny(experts=8 * world if world <= 4 else 16, layers=3, topk=512)
+    cfg = DsaMoeConfig().tiny(experts=8 * world if world <= 4 else 16, layers=3, topk=512,
+                               dense_ffn=max(512, 128 * world))   # every rank's FFN shard is a whole 128-column block
     B, prompt, steps = 4, 300, 3
 
     def run(mode, w, r, grp, cgrp, routing=None, **kw):

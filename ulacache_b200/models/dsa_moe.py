@@ -407,6 +407,8 @@ class DsaMoeModel:
             from ..ops import topk as _topk
 
             self._topk_ws = _topk.workspace(max_batch, self.device)
+        self._nvtx = _os.environ.get("ULC_NVTX", "0") == "1"
+        self._nvtx_open = False
         self.record_selections = None       # a list here makes every layer append its selected record IDs
         self.record_sublayers = None        # ... and (attention output, feed-forward output) of every layer
         self.record_routing = None          # ... and (expert choice, gate) of every MoE layer
@@ -459,7 +461,17 @@ class DsaMoeModel:
         self._prof = {} if on else None
 
     def _mark(self, name: str):
-        """Close the running section and open ``name`` (no-op unless profiling)."""
+        """Close the running section and open ``name``: a CUDA-event section when profiling, and an
+        NVTX range when ``ULC_NVTX=1`` (ranges nest under the step's range and show up in any
+        NVTX-aware timeline; they are recorded during graph capture only as host markers)."""
+        if self._nvtx:
+            import torch
+
+            if self._nvtx_open:
+                torch.cuda.nvtx.range_pop()
+            self._nvtx_open = name != "end"              # "end" closes the step's last section
+            if self._nvtx_open:
+                torch.cuda.nvtx.range_push(name)
         prof = getattr(self, "_prof", None)
         if prof is None:
             return

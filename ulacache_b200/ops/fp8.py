@@ -228,6 +228,8 @@ def pick_splits(nout: int, k: int, experts: int = 1, sm_count: int = 148) -> int
     clearing and converting the fp32 accumulation buffer."""
     tiles = (nout // 128) * experts
     kb = k // 128
+    if kb < 1 or nout < 128:
+        raise ValueError("fp8 block-scaled GEMMs need at least one 128 x 128 block")
     if tiles >= sm_count:
         return 1
     best, best_cost = 1, None
