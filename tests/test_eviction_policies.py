@@ -172,3 +172,20 @@ def test_bitmap_ring_takes_the_bucket_ring_decisions():
     for step in range(50):
         ids = [rng.randrange(1, 30) for _ in range(5)]
         assert c.step(ids) == d.step(ids)
+
+
+def test_parallel_ring_policy_cpu_semantics():
+    """Transaction semantics of the parallel ring's CPU twin: hits are pinned before victims are chosen,
+    victims are the oldest (cold first), lowest slot first; epochs before the first advance count."""
+    import torch
+    from ulacache_b200.eviction import ParallelPresenceRingPolicy
+
+    pol = ParallelPresenceRingPolicy(4, 32, "cpu")
+    assert pol.step(torch.tensor([1, 2, 3, 4]))[:2] == (0, 4)          # fills slots 0..3
+    h, m, ev = pol.step(torch.tensor([9, 1]))                          # 1 is hit AFTER 9 in the list, yet pinned first
+    assert (h, m) == (1, 1) and ev.tolist() == [2]                     # victim: lowest untouched slot (slot 1 = id 2)
+    h, m, ev = pol.step(torch.tensor([3, 10, 11]))
+    assert (h, m) == (1, 2) and ev.tolist() == [4, 1]                  # id 4 (epoch 1) is the oldest; then epoch 2's lowest slot (slot 0 = id 1)
+    assert pol.totals == dict(hits=2, misses=7, evictions=3, overflow=0)
+    h, m, ev = pol.step(torch.tensor([20, 21, 22, 23, 24]))            # more misses than evictable slots
+    assert m == 5 and len(ev) == 4 and pol.totals["overflow"] == 1

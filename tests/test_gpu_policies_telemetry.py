@@ -110,3 +110,30 @@ def test_replay_probes_and_miss_trace_match_the_host_path(native):
         snaps.append(tr.snapshot_chunk())
     for key in snaps[0]:
         assert torch.equal(snaps[0][key], snaps[1][key]), key
+
+
+def test_parallel_presence_ring_matches_its_cpu_twin_step_by_step(native):
+    """Parallel bitmap ring on the device == the transaction-semantics oracle, eviction by eviction, over
+    more than two rotations of the 255-bucket ring (cold bucket, drains and stale summaries included)."""
+    from ulacache_b200.eviction import ParallelPresenceRingPolicy
+
+    rng = random.Random(4)
+    capacity, id_space = 700, 5000
+    cpu = ParallelPresenceRingPolicy(capacity, id_space, "cpu")
+    gpu = ParallelPresenceRingPolicy(capacity, id_space, "cuda")
+    hot = list(range(200))
+    for step in range(600):
+        n_cold = 3 if step % 50 else 400                   # bursts force evictions deep into old buckets
+        ids = sorted(set(rng.sample(hot, 60)) | set(rng.sample(range(id_space), n_cold)))
+        rng.shuffle(ids)
+        t = torch.tensor(ids, dtype=torch.int32)
+        a, b = cpu.step(t), gpu.step(t)
+        assert a[:2] == b[:2], step
+        assert a[2].tolist() == b[2].cpu().tolist(), step
+    assert cpu.totals == gpu.totals and gpu.totals["evictions"] > 1000
+    # the device directory and the twin's agree
+    assert torch.equal(cpu.dir, gpu.dir.cpu()) and torch.equal(cpu.id_of, gpu.id_of.cpu())
+    ring = gpu.ring
+    assert int(ring.count.sum()) == capacity - gpu.nfree
+    pop = sum(bin(int(w) & 0xffffffff).count("1") for w in ring.bits.cpu().flatten().tolist())
+    assert pop == capacity - gpu.nfree

@@ -225,8 +225,9 @@ __global__ void trace_hits_kernel(const int32_t* __restrict__ dir, int dir_len, 
 // holds kPresenceBuckets bitmaps of presence_words(capacity) words, `inverse` one entry per slot.
 // state[0] = free-stack height, state[1] = 1 once the ring is initialised.
 __global__ void presence_ring_step_kernel(PresenceRing* ring, uint32_t* bits, int16_t* inverse, int capacity,
-                                          int32_t* dir, int32_t* id_of, int32_t* free_stack, int32_t* state,
-                                          const int32_t* ids, int n, int32_t* evicted, int32_t* counts) {
+                                          int32_t* dir, int id_space, int32_t* id_of, int32_t* free_stack, int32_t* state,
+                                          const int32_t* ids, int n, int32_t* evicted, int32_t* counts,
+                                          int32_t* status) {
   if (threadIdx.x != 0 || blockIdx.x != 0) return;
   if (state[1] == 0) {            // `bits` arrives zeroed
     ring->init(bits, inverse, capacity);
@@ -237,6 +238,10 @@ __global__ void presence_ring_step_kernel(PresenceRing* ring, uint32_t* bits, in
   int hits = 0, misses = 0, ev = 0, overflow = 0;
   for (int i = 0; i < n; ++i) {
     const int id = ids[i];
+    if (id < 0 || id >= id_space) {      // reported, never dereferenced
+      report(status, kErrBounds, id);
+      continue;
+    }
     int s = dir[id];
     if (s >= 0) {
       ++hits;
@@ -295,12 +300,13 @@ long long ulc_presence_ring_words(int capacity) {
   return static_cast<long long>(ulc::kPresenceBuckets) * ulc::presence_words(capacity);
 }
 
-int ulc_ablate_presence_ring_step(void* ring, uint32_t* bits, int16_t* inverse, int capacity, int32_t* dir,
+int ulc_ablate_presence_ring_step(void* ring, uint32_t* bits, int16_t* inverse, int capacity, int32_t* dir, int id_space,
                                   int32_t* id_of, int32_t* free_stack, int32_t* state, const int32_t* ids, int n,
-                                  int32_t* evicted, int32_t* counts, cudaStream_t stream) {
-  if (capacity <= 0) return -ulc::kErrUnsupported;
+                                  int32_t* evicted, int32_t* counts, int32_t* status, cudaStream_t stream) {
+  if (capacity <= 0 || id_space <= 0) return -ulc::kErrUnsupported;
   ulc::presence_ring_step_kernel<<<1, 32, 0, stream>>>(static_cast<ulc::PresenceRing*>(ring), bits, inverse, capacity,
-                                                        dir, id_of, free_stack, state, ids, n, evicted, counts);
+                                                        dir, id_space, id_of, free_stack, state, ids, n, evicted, counts,
+                                                        status);
   return static_cast<int>(cudaGetLastError());
 }
 

@@ -162,6 +162,7 @@ struct PresenceRing {
     const int64_t per = presence_words(slots);
     for (int b = 0; b < kPresenceBuckets; ++b) bucket[b].init(bits + per * b, slots);
     for (int b = 0; b < kPresenceRecent; ++b) bucket_epoch[b] = -1;
+    bucket_epoch[0] = 0;                 // slots touched before the first advance() belong to epoch 0
     for (int32_t s = 0; s < slots; ++s) inverse[s] = kPresenceFree;
   }
 

@@ -10,5 +10,5 @@ launch_config.py.
 """
 from .launch_config import LaunchConfig, victim_launch_config  # noqa: F401
 from .oracle import POLICY_KINDS, PolicyOracle, replay_trace  # noqa: F401
-from .policies import (ExactLruPolicy, HotBufferPolicy, LinkedListLruPolicy, PresenceRingPolicy,  # noqa: F401
-                       trace_hits)
+from .policies import (ExactLruPolicy, HotBufferPolicy, LinkedListLruPolicy, ParallelPresenceRing,  # noqa: F401
+                       ParallelPresenceRingPolicy, PresenceRingPolicy, trace_hits)

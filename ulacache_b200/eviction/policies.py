@@ -158,6 +158,7 @@ class PresenceRingPolicy:
         self.id_of = torch.full((capacity,), -1, **i32)
         self.free_stack = torch.arange(capacity - 1, -1, -1, **i32)            # lowest slot on top
         self.state = torch.tensor([capacity, 0], **i32)                        # free height, initialised flag
+        self.status = N.new_status(device)
 
     def step(self, ids):
         import torch
@@ -173,10 +174,169 @@ class PresenceRingPolicy:
             cnt = torch.zeros(4, dtype=torch.int32, device=self.dir.device)
             N.check(N.cuda().ulc_ablate_presence_ring_step(
                 N.ptr(self.ring), N.ptr(self.bits), N.ptr(self.inverse), C.c_int(self.capacity), N.ptr(self.dir),
-                N.ptr(self.id_of), N.ptr(self.free_stack), N.ptr(self.state), N.ptr(ids32), C.c_int(n),
-                N.ptr(evicted_buf), N.ptr(cnt), N.stream()), "presence_ring_step")
+                C.c_int(self.dir.numel()), N.ptr(self.id_of), N.ptr(self.free_stack), N.ptr(self.state), N.ptr(ids32),
+                C.c_int(n), N.ptr(evicted_buf), N.ptr(cnt), N.ptr(self.status), N.stream()), "presence_ring_step")
             h, m, e, over = (int(x) for x in cnt.tolist())
+            N.raise_on_status(self.status, "presence ring step")
             evicted = evicted_buf[:e]
+        self.totals["hits"] += h
+        self.totals["misses"] += m
+        self.totals["evictions"] += int(evicted.numel())
+        self.totals["overflow"] += over
+        return h, m, evicted
+
+
+class _PRing(C.Structure):
+    _fields_ = [("bits", C.c_void_p), ("summary", C.c_void_p), ("slot_bucket", C.c_void_p), ("count", C.c_void_p),
+                ("bucket_epoch", C.c_void_p), ("ctl", C.c_void_p), ("vlist", C.c_void_p), ("chunk_count", C.c_void_p),
+                ("n", C.c_int32), ("w0", C.c_int32), ("w1", C.c_int32)]
+
+
+class ParallelPresenceRing:
+    """Device state and launches of the parallel presence-bitmap ring (``csrc/presence_ring.cu``):
+    ``advance`` / ``touch`` / ``detach`` / ``victims`` on slot numbers, usable by any directory.
+
+    Reference: ulacache/eviction/lru.py:132 (create_presence_ring), csrc/eviction/presence_recent.cuh:52-229,
+    presence_warp.cuh:11-133, victims.cuh:81-194."""
+
+    def __init__(self, slots: int, device):
+        import torch
+
+        N = _n()
+        w0, w1 = C.c_int(0), C.c_int(0)
+        N.check(N.cuda().ulc_pring_words(C.c_int(slots), C.byref(w0), C.byref(w1)), "pring_words")
+        self.slots, self.w0, self.w1 = slots, w0.value, w1.value
+        i32 = dict(dtype=torch.int32, device=device)
+        self.bits = torch.zeros((256, self.w0), **i32)
+        self.summary = torch.zeros((256, self.w1), **i32)
+        self.slot_bucket = torch.full((slots,), -1, **i32)
+        self.count = torch.zeros(256, **i32)
+        self.bucket_epoch = torch.full((255,), -1, **i32)
+        self.bucket_epoch[0] = 0                      # slots touched before the first advance belong to epoch 0
+        self.ctl = torch.zeros(8, **i32)
+        self.vlist = torch.zeros((256, 3), **i32)
+        self.chunk_count = torch.zeros((256, 256), **i32)          # [bucket list entry][chunk]
+        self.status = N.new_status(device)
+        self.struct = _PRing(self.bits.data_ptr(), self.summary.data_ptr(), self.slot_bucket.data_ptr(),
+                             self.count.data_ptr(), self.bucket_epoch.data_ptr(), self.ctl.data_ptr(),
+                             self.vlist.data_ptr(), self.chunk_count.data_ptr(), slots, self.w0, self.w1)
+
+    @property
+    def metadata_bytes(self) -> int:
+        return sum(t.numel() * 4 for t in (self.bits, self.summary, self.slot_bucket, self.count, self.bucket_epoch,
+                                           self.ctl, self.vlist, self.chunk_count))
+
+    def advance(self):
+        N = _n()
+        N.check(N.cuda().ulc_pring_advance(C.byref(self.struct), N.stream()), "pring_advance")
+
+    def touch(self, slots, detach: bool = False):
+        N = _n()
+        N.check(N.cuda().ulc_pring_touch(C.byref(self.struct), N.ptr(slots), C.c_int(slots.numel()), C.c_int(int(detach)),
+                                         N.ptr(self.status), N.stream()), "pring_touch")
+
+    def victims(self, need: int, out):
+        """Writes the victims (eviction order: cold bucket first, then the oldest recent buckets, lowest slot
+        first inside a bucket; never a slot of the current epoch) to ``out``; ``ctl[2]`` holds how many."""
+        N = _n()
+        N.check(N.cuda().ulc_pring_victims(C.byref(self.struct), C.c_int(need), N.ptr(out), C.c_int(out.numel()),
+                                           N.stream()), "pring_victims")
+
+    @property
+    def served(self) -> int:
+        return int(self.ctl[2])
+
+
+class ParallelPresenceRingPolicy:
+    """Replay policy on the parallel presence-bitmap ring.  A step is a transaction, as in the residency
+    kernels: every hit is touched first, then the misses are placed in input order (free slots, then
+    victims), so a record accessed in this step is never evicted by it.  CPU tensors run the same
+    semantics in Python (the oracle of the GPU test)."""
+
+    def __init__(self, capacity: int, id_space: int, device):
+        import torch
+
+        self.capacity, self.id_space = capacity, id_space
+        self.device = torch.device(device)
+        self.totals = dict(hits=0, misses=0, evictions=0, overflow=0)
+        i32 = dict(dtype=torch.int32, device=device)
+        self.dir = torch.full((id_space,), -1, **i32)
+        self.id_of = torch.full((capacity,), -1, **i32)
+        self.free_stack = torch.arange(capacity - 1, -1, -1, **i32)            # lowest slot on top
+        self.nfree = capacity
+        self.epoch = 0
+        if self.device.type == "cuda":
+            self.ring = ParallelPresenceRing(capacity, device)
+        else:
+            self.stamp = [-1] * capacity
+
+    def _cpu_step(self, ids):
+        import torch
+
+        self.epoch += 1
+        dir_, id_of = self.dir, self.id_of
+        misses = []
+        hits = 0
+        for rid in ids.tolist():
+            s = int(dir_[rid])
+            if s >= 0:
+                hits += 1
+                self.stamp[s] = self.epoch
+            else:
+                misses.append(rid)
+        from_free = min(len(misses), self.nfree)
+        need = len(misses) - from_free
+        live = [s for s in range(self.capacity) if int(id_of[s]) >= 0 and self.stamp[s] != self.epoch]
+        live.sort(key=lambda s: (-min(self.epoch - self.stamp[s], 255), s))
+        victims = live[:need]
+        evicted = []
+        for i, rid in enumerate(misses[: from_free + len(victims)]):
+            if i < from_free:
+                s = int(self.free_stack[self.nfree - 1 - i])
+            else:
+                s = victims[i - from_free]
+                evicted.append(int(id_of[s]))
+                dir_[int(id_of[s])] = -1
+            id_of[s] = rid
+            dir_[rid] = s
+            self.stamp[s] = self.epoch
+        self.nfree -= from_free
+        return hits, len(misses), torch.tensor(evicted, dtype=torch.int32), len(misses) - from_free - len(victims)
+
+    def step(self, ids):
+        """``ids``: distinct record ids accessed this step -> (hits, misses, evicted ids in eviction order)."""
+        import torch
+
+        if self.device.type != "cuda":
+            h, m, evicted, over = self._cpu_step(ids)
+        else:
+            N = _n()
+            ring = self.ring
+            ids32 = ids.to(self.device).to(torch.int32).contiguous()
+            n = int(ids32.numel())
+            self.epoch += 1
+            ring.advance()
+            flags = torch.empty(n, dtype=torch.int32, device=self.device)
+            N.check(N.cuda().ulc_pring_lookup_touch(C.byref(ring.struct), N.ptr(ids32), C.c_int(n), N.ptr(self.dir),
+                                                    C.c_int(self.id_space), N.ptr(flags), N.ptr(ring.status), N.stream()),
+                    "pring_lookup_touch")
+            miss_ids = ids32[flags.bool()].contiguous()            # input order (stable compaction)
+            m = int(miss_ids.numel())
+            h = n - m
+            from_free = min(m, self.nfree)
+            need = m - from_free
+            victims = torch.empty(max(need, 1), dtype=torch.int32, device=self.device)
+            ring.victims(need, victims)
+            served = ring.served if need else 0
+            evicted = torch.empty(max(served, 1), dtype=torch.int32, device=self.device)
+            N.check(N.cuda().ulc_pring_place(C.byref(ring.struct), N.ptr(miss_ids), C.c_int(from_free + served),
+                                             C.c_int(from_free), N.ptr(self.free_stack), C.c_int(self.nfree),
+                                             N.ptr(victims), N.ptr(self.dir), N.ptr(self.id_of), N.ptr(evicted),
+                                             N.stream()), "pring_place")
+            self.nfree -= from_free
+            evicted = evicted[:served]
+            over = need - served
+            N.raise_on_status(ring.status, "presence ring")
         self.totals["hits"] += h
         self.totals["misses"] += m
         self.totals["evictions"] += int(evicted.numel())

@@ -20,6 +20,59 @@ import math
 import random
 
 
+def ttft(args):
+    """Time to first token of one request: the prompt goes through the model in chunks of
+    ``--prefill-chunk`` rows (every row selects and attends with its own causal length), then one token
+    is sampled.  Wall clock around the chunks with a synchronize on both sides, after a warm-up request of
+    two chunks; reported with the chunk count and the per-chunk time."""
+    import time
+
+    import torch
+    from ..models.dsa_moe import DsaMoeConfig
+    from ..serving.server import ServingEngine
+
+    n = args.ttft_prompt
+    cfg = (DsaMoeConfig().tiny(layers=args.layers, topk=256) if args.tiny
+           else DsaMoeConfig(layers=args.layers, unique_layer_weights=min(args.layers, args.unique_layers)))
+    records = (n + 4 * args.prefill_chunk + 4096) // 64 * 64
+    srv = ServingEngine(cfg, max_batch=args.max_batch, max_context=n + 64, device_records=records, host_records=0,
+                        prefill_chunk=args.prefill_chunk)
+    import random
+
+    rng = random.Random(0)
+    warm = [rng.randrange(cfg.vocab) for _ in range(min(n, 2 * args.prefill_chunk))]
+    srv.submit(0, warm, 1, 0.0)
+    while srv.busy():
+        srv.step()
+    torch.cuda.synchronize()
+    prompt = [rng.randrange(cfg.vocab) for _ in range(n)]
+    t0 = time.perf_counter()
+    srv.clock = lambda: time.perf_counter() - t0
+    srv.finished.clear()
+    srv.submit(1, prompt, 1, 0.0)
+    steps = 0
+    sections = None
+    while srv.busy():
+        if args.sections and steps == args.sections:        # per-section device time of ONE chunk
+            srv.model.enable_profile(True)
+        srv.step()
+        if args.sections and steps == args.sections:
+            sections = {k: round(v, 2) for k, v in srv.model.profile_summary().items()}
+            srv.model.enable_profile(False)
+        steps += 1
+    torch.cuda.synchronize()
+    r = srv.finished[-1]
+    if sections is not None:
+        print(json.dumps(dict(experiment="ttft_chunk_sections_ms", chunk_index=args.sections, sections=sections)))
+    out = dict(experiment="ttft", prompt_tokens=n, prefill_chunk=args.prefill_chunk, layers=cfg.layers,
+               distinct_layer_weight_sets_resident=cfg.unique_layer_weights or cfg.layers, chunks=steps,
+               ttft_s=round(r.first_token_time - r.arrival, 4),
+               ms_per_chunk=round(1e3 * (r.first_token_time - r.arrival) / max(1, steps), 2),
+               prompt_tokens_per_s=round(n / (r.first_token_time - r.arrival), 1), model="tiny" if args.tiny else "full width")
+    print(json.dumps(out))
+    srv.close()
+
+
 def build_trace(*, sessions, turns_lo, turns_hi, system_prefix, median_input, sigma, input_cap, out_lo, out_hi, rate,
                 vocab, seed=0):
     rng = random.Random(seed)
@@ -62,7 +115,14 @@ def main():
     ap.add_argument("--prefill-chunk", type=int, default=64)
     ap.add_argument("--device-records", type=int, default=32768)
     ap.add_argument("--host-multiple", type=float, default=2.0, help="host tier size as a multiple of the device tier")
+    ap.add_argument("--ttft-prompt", type=int, default=0,
+                    help="instead of the replay: time to first token of ONE request with this many prompt tokens")
+    ap.add_argument("--sections", type=int, default=0,
+                    help="with --ttft-prompt: also print the per-section device time of this chunk (0 = off)")
+    ap.add_argument("--unique-layers", type=int, default=4, help="distinct layer weight sets kept resident (cycled)")
     args = ap.parse_args()
+    if args.ttft_prompt:
+        return ttft(args)
     cfg = DsaMoeConfig().tiny(layers=args.layers, topk=256) if args.tiny else DsaMoeConfig(layers=args.layers, unique_layer_weights=min(args.layers, 4))
     tl, th = (int(x) for x in args.turns.split(","))
     ol, oh = (int(x) for x in args.output.split(","))

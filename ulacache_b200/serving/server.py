@@ -153,9 +153,19 @@ class ServingEngine:
         i32 = dict(dtype=torch.int32, device=self.device)
         tokens = torch.tensor([t for _, t, _ in rows], **i32)
         lengths = torch.tensor([p for _, _, p in rows], **i32)
-        pages = torch.full((len(rows), self.max_pages), -1, **i32)
-        for i, (r, _, _) in enumerate(rows):
-            pages[i, : len(r.pages)] = torch.tensor(r.pages, **i32)
+        # one page-table row per distinct request, expanded to its rows (a prefill chunk is thousands of
+        # rows of one request)
+        order, index = {}, []
+        for r, _, _ in rows:
+            index.append(order.setdefault(id(r), len(order)))
+        table = torch.full((len(order), self.max_pages), -1, dtype=torch.int32)
+        seen = set()
+        for r, _, _ in rows:
+            k = order[id(r)]
+            if k not in seen:
+                seen.add(k)
+                table[k, : len(r.pages)] = torch.tensor(r.pages, dtype=torch.int32)
+        pages = table.to(self.device)[torch.tensor(index, device=self.device)]
         return DecodeBatch(tokens=tokens, lengths=lengths, req_pages=pages, out_tokens=torch.zeros(len(rows), **i32))
 
     def step(self):
