@@ -112,7 +112,7 @@ def main():
     ap.add_argument("--layers", type=int, default=4)
     ap.add_argument("--tiny", action="store_true", help="the small test model instead of the full-width one")
     ap.add_argument("--max-batch", type=int, default=16)
-    ap.add_argument("--prefill-chunk", type=int, default=64)
+    ap.add_argument("--prefill-chunk", type=int, default=512)
     ap.add_argument("--device-records", type=int, default=32768)
     ap.add_argument("--host-multiple", type=float, default=2.0, help="host tier size as a multiple of the device tier")
     ap.add_argument("--ttft-prompt", type=int, default=0,

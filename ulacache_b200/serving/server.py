@@ -53,7 +53,7 @@ def percentile(values, p):
 
 class ServingEngine:
     def __init__(self, cfg, *, max_batch: int, max_context: int, device_records: int, host_records: int = 0,
-                 prefill_chunk: int = 64, device=None, seed: int = 0, clock=time.perf_counter):
+                 prefill_chunk: int = 512, device=None, seed: int = 0, clock=time.perf_counter):
         import torch
         from .. import client
         from ..bindings import LocalCacheBindings
