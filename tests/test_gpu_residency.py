@@ -92,3 +92,32 @@ def test_cache_api_on_cuda_with_host_tier(native):
     assert c["promotions"] > 0 and c["evictions"] > 0 and c["unserved"] == 0
     cache.free(ids)
     cache.close()
+
+
+def test_receive_leases_and_publication_on_the_device(native):
+    """Lease kernels == the CPU path (leased slots are never victims, last release re-attaches), and the
+    publication kernel copies every layer of every record to its tier."""
+    import torch
+    from test_receive_and_tools import _lease_scenario, _leased_residency
+
+    cpu, gpu = _lease_scenario("cpu"), _lease_scenario("cuda")
+    for key in ("loc", "ring_leased", "still_leased", "stamps", "ring_after", "leases"):
+        assert cpu[key] == gpu[key], key
+    assert len(gpu["victims"]) == 3 and not set(gpu["victims"]) & {gpu["loc"][0], gpu["loc"][1]}
+    res, ids, leases = _leased_residency("cuda")
+    loc = leases.acquire(ids[[2, 10, 5, 11]])
+    staging = torch.randint(0, 255, (5, 6, 656), dtype=torch.uint8, device="cuda")
+    dev_plane = torch.zeros(5, 8, 656, dtype=torch.uint8, device="cuda")
+    host_plane = torch.zeros(5, 16, 656, dtype=torch.uint8).pin_memory()
+    rows = torch.tensor([3, 0, 1, 5])
+    leases.publish(staging, rows, loc, dev_plane, host_plane)
+    torch.cuda.synchronize()
+    res.check_status("publish")
+    for i, r in enumerate(rows.tolist()):
+        e = int(loc[i])
+        got = dev_plane[:, e].cpu() if e >= 0 else host_plane[:, -e - 2]
+        assert torch.equal(got, staging[:, r].cpu()), i
+    leases.release(ids[[2, 10, 5, 11]], loc)
+    torch.cuda.synchronize()
+    res.check_status("release")
+    assert int(leases.leases.sum()) == 0

@@ -114,3 +114,66 @@ def test_direct_receiver_places_bytes_into_canonical_records():
     cache.finish_layer_attention(1)
     cache.finish_model_forward()
     cache.close()
+
+
+def _leased_residency(device):
+    import torch
+    from ulacache_b200.cache.residency import ResidencyGeometry, make_residency
+    from ulacache_b200.storage.layout import OwnerMap
+    from ulacache_b200.transfer.receive_lease import ReceiveLeases
+
+    res = make_residency(ResidencyGeometry(dir_len=512, hbm_slots=8, host_slots=16, plan_capacity=16), OwnerMap(1, 6), 0, device)
+    ids = torch.arange(1, 13, dtype=torch.int32, device=device)          # 8 land in HBM, 4 on the host
+    res.begin_step()
+    res.register(ids)
+    return res, ids, ReceiveLeases(res)
+
+
+def _lease_scenario(device):
+    """Leased device slots cannot be victims; the last release re-attaches them as touched now."""
+    import torch
+    from ulacache_b200.cache.residency import CNT_PLAN
+
+    res, ids, leases = _leased_residency(device)
+    incoming = ids[[0, 1, 9]]                                            # two device rows and a host row
+    loc = leases.acquire(incoming)
+    loc2 = leases.acquire(incoming[:1])                                  # a second writer on the first row
+    ring_leased = int(res.ring.sum())
+    # a later step wants three promotions: with slots 0 and 1 leased, victims must come from the other six
+    for _ in range(2):
+        res.begin_step()
+    res.pin(ids[8:11])                                                   # three host rows -> three promotions
+    res.plan_step()
+    n = int(res.counters[CNT_PLAN])
+    victims = res.plan[1, :n].cpu().tolist()
+    leases.release(incoming[:1], loc2)
+    still = int(res.stamps[int(loc[0])])
+    leases.release(incoming, loc)
+    out = dict(loc=loc.cpu().tolist(), ring_leased=ring_leased, victims=sorted(victims), still_leased=still,
+               stamps=[int(res.stamps[int(loc[0])]), int(res.stamps[int(loc[1])])], ring_after=int(res.ring.sum()),
+               leases=int(leases.leases.sum()))
+    if hasattr(res, "check_status"):
+        res.check_status("receive leases")
+    return out
+
+
+def test_receive_leases_cpu():
+    out = _lease_scenario("cpu")
+    assert out["loc"][0] >= 0 and out["loc"][1] >= 0 and out["loc"][2] <= -2
+    assert out["ring_leased"] == 6 and out["still_leased"] == -2 and out["leases"] == 0
+    assert len(out["victims"]) == 3 and not set(out["victims"]) & {out["loc"][0], out["loc"][1]}
+    assert out["stamps"] == [3, 3] and out["ring_after"] == 8
+
+
+def test_publish_copies_to_both_tiers_cpu():
+    import torch
+    from ulacache_b200.transfer.receive_lease import ReceiveLeases
+
+    res, ids, leases = _leased_residency("cpu")
+    loc = leases.acquire(ids[[2, 10, 5]])
+    staging = torch.randint(0, 255, (3, 4, 656), dtype=torch.uint8)
+    dev_plane, host_plane = torch.zeros(3, 8, 656, dtype=torch.uint8), torch.zeros(3, 16, 656, dtype=torch.uint8)
+    leases.publish(staging, torch.tensor([3, 0, 1]), loc, dev_plane, host_plane)
+    assert torch.equal(dev_plane[:, int(loc[0])], staging[:, 3]) and torch.equal(dev_plane[:, int(loc[2])], staging[:, 1])
+    assert torch.equal(host_plane[:, -int(loc[1]) - 2], staging[:, 0])
+    assert int(dev_plane.sum()) == int(staging[:, 3].sum()) + int(staging[:, 1].sum())

@@ -114,3 +114,24 @@ def test_entry_point_writes_the_startup_receipt(tmp_path):
     rep = json.loads(out.stdout.strip().splitlines()[-1])
     assert rep["ranks"] == 2 and rep["device_records"] == 2 * 1024 and rep["host_records"] == 2 * 3136
     assert rep["unique_kv_records"] == rep["device_records"] + rep["host_records"]
+
+
+def test_launcher_resolves_methods_and_capacity(capsys):
+    """The per-method launcher: layouts, tier sizes and the capacity each method admits under one budget."""
+    from ulacache_b200.serving import launch
+
+    ns = lambda **kw: __import__("argparse").Namespace(**dict(dict(
+        method="ulacache", mode="dpa", batch_per_gpu=32, prompt_len=32768, max_new_tokens=64, layers=0, hot_buffer=4096,
+        host_fraction=0.0, kv_budget_hbm_gb=64.0, kv_budget_host_gb=128.0), **kw))
+    dpa = launch.resolve(ns(), 8)
+    assert (dpa["mode"], dpa["kv_layout"], dpa["batch_per_engine"], dpa["global_batch"]) == ("dpa", "pooled", 32, 256)
+    tp = launch.resolve(ns(mode="tp"), 8)
+    assert tp["batch_per_engine"] == 256 and tp["records_per_rank"] < dpa["records_per_rank"] * 1.02
+    hic = launch.resolve(ns(method="hicache"), 8)
+    assert (hic["mode"], hic["kv_layout"]) == ("tp", "replicated") and hic["records_per_rank"] > 7.9 * tp["records_per_rank"]
+    his = launch.resolve(ns(method="hisparse"), 8)
+    assert his["device_record_capacity"] == 256 * 4096 and his["host_record_capacity"] > his["records_per_rank"] - 256 * 4096
+    cap = {m: launch.capacity(ns(method=m), 8)["tokens_admitted"] for m in launch.METHODS}
+    assert cap["ulacache"] == 8 * cap["hicache"] and cap["hisparse"] < cap["hicache"]
+    assert launch.main(["--method", "hicache", "--dry-run"]) == 0
+    assert '"kv_layout": "replicated"' in capsys.readouterr().out

@@ -162,7 +162,8 @@ def main():
     single_logits, single_toks, single_routes = run("dpa", 1, 0, None, None)
     vl = (cfg.vocab + world - 1) // world
     for name, mode, kw in (("dpa", "dpa", {}), ("tp_owner", "tp", dict(tp_attention="owner")),
-                           ("tp_gather", "tp", dict(tp_attention="gather"))):
+                           ("tp_gather", "tp", dict(tp_attention="gather")),
+                           ("tp_replicated", "tp", dict(kv_layout="replicated"))):     # the replicated-KV baseline arm
         logits, toks, _ = run(mode, world, rank, group, cpu_group, routing=single_routes, **kw)
         ok = True
         worst = rms = 0.0

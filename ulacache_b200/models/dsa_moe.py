@@ -311,11 +311,13 @@ class DsaMoeModel:
     def __init__(self, cfg: DsaMoeConfig, *, device, cache, index_pool, tp: int = 1, rank: int = 0,
                  group=None, cpu_group=None, mode: str = "tp", max_batch: int = 64, max_context: int = 65536,
                  seed: int = 0, comm: str = "peer", deterministic: Optional[bool] = None,
-                 tp_attention: str = "owner", weights_from_full: bool = False):
+                 tp_attention: str = "owner", weights_from_full: bool = False, kv_layout: str = "pooled"):
         import torch
         from ..ops import _native as N
         from ..ops import records
 
+        if kv_layout not in ("pooled", "replicated"):
+            raise ValueError("kv_layout must be pooled or replicated")
         if mode not in ("tp", "dpa"):
             raise ValueError("mode must be tp or dpa")
         if cfg.heads % tp or cfg.experts % tp:
@@ -336,7 +338,11 @@ class DsaMoeModel:
         if hint:
             _Fp8Linear.rows_hint = int(hint)
         self.attn_tp = tp if mode == "tp" else 1          # heads are sharded only in tp mode
-        self.kv_ranks = tp if mode == "tp" else 1         # owners of the striped pool
+        # owners of the striped pool.  ``kv_layout="replicated"`` is the baseline a pooled cache is measured
+        # against: tensor-parallel heads, but every rank keeps (and writes) ALL records and index keys, so
+        # attention and the indexer are rank-local and the KV capacity is that of one GPU
+        self.kv_ranks = tp if (mode == "tp" and kv_layout == "pooled") else 1
+        self.kv_rank = rank if self.kv_ranks > 1 else 0
         self.dpa = mode == "dpa" and tp > 1               # tokens gathered / scattered around the experts
         # tensor-parallel attention over the striped pool: "gather" = every rank reads all selected
         # records (peers' pools included) for its own heads; "owner" = every rank attends over the
@@ -344,7 +350,7 @@ class DsaMoeModel:
         if tp_attention not in ("owner", "gather"):
             raise ValueError("tp_attention must be owner or gather")
         self.owner_attention = (mode == "tp" and tp > 1 and tp_attention == "owner" and comm == "peer"
-                                and self.device.type == "cuda")
+                                and self.device.type == "cuda" and self.kv_ranks > 1)
         self.max_batch, self.max_context = max_batch, max_context
         gen = torch.Generator(device=self.device).manual_seed(seed)
         shard_gen = torch.Generator(device=self.device).manual_seed(seed + 7919 * (rank + 1))
@@ -386,7 +392,7 @@ class DsaMoeModel:
         self.index_pool = index_pool                                              # uint8 [layers, pages, 8448]
         self.index_views = [records.make_index_view(page_ptrs=[index_pool[l].data_ptr()] * max(self.kv_ranks, 1),
                                                     pages_per_rank=index_pool.shape[1], ranks=self.kv_ranks,
-                                                    my_rank=rank if mode == "tp" else 0)
+                                                    my_rank=self.kv_rank)
                             for l in range(cfg.cache_layers)]
         # multi-token-prediction draft: h' = W [norm(emb(next token)); norm(h)] -> one decoder layer -> shared head
         self.mtp = None
@@ -595,7 +601,7 @@ class DsaMoeModel:
                                 positions=batch.lengths, owner_only=True, status=self.status)
         self._mark("index.score")
         logits = indexer.index_score(iq8, iwf, batch.req_pages, self._ctx, self.index_pool[layer],
-                                     ranks=self.kv_ranks, rank=self.rank if self.mode == "tp" else 0,
+                                     ranks=self.kv_ranks, rank=self.kv_rank,
                                      status=self.status, topk_workspace=self._topk_ws)
         self._mark("index.topk")
         sel = self._select(logits, batch)

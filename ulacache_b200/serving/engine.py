@@ -54,7 +54,7 @@ class DecodeEngine:
                  host_record_capacity: int = 0, device_record_capacity: Optional[int] = None,
                  use_graph: bool = True, seed: int = 0,
                  kv_transport: str = "auto", comm: str = "peer", spec_steps: int = 3, force_accept=None,
-                 tp_attention: str = "owner", weights_from_full: bool = False):
+                 tp_attention: str = "owner", weights_from_full: bool = False, kv_layout: str = "pooled"):
         import torch
         from .. import client
         from ..bindings import LocalCacheBindings, TensorParallelCacheBindings
@@ -67,7 +67,8 @@ class DecodeEngine:
         self.cfg, self.mode, self.rank, self.world = cfg, mode, rank, world
         self.device = torch.device("cuda", local_rank)
         torch.cuda.set_device(self.device)
-        kv_ranks = world if mode == "tp" else 1
+        kv_ranks = world if (mode == "tp" and kv_layout == "pooled") else 1
+        self.kv_ranks, self.kv_layout = kv_ranks, kv_layout
         span = 64 * kv_ranks
         # speculative decoding: rows per request in the verify pass, and room for rejected drafts
         self.spec_steps = spec_steps if cfg.mtp_layers else 0
@@ -104,7 +105,7 @@ class DecodeEngine:
         self.model = DsaMoeModel(cfg, device=self.device, cache=self.cache, index_pool=self.index_pool, tp=world,
                                  rank=rank, group=group, cpu_group=cpu_group, mode=mode, max_batch=batch * rows_per_request,
                                  max_context=total + 8, seed=seed, comm=comm, tp_attention=tp_attention,
-                                 weights_from_full=weights_from_full)
+                                 weights_from_full=weights_from_full, kv_layout=kv_layout)
         i32 = dict(dtype=torch.int32, device=self.device)
         self.batch = DecodeBatch(tokens=torch.zeros(batch, **i32), lengths=torch.zeros(batch, **i32),
                                  req_pages=torch.full((batch, pages), -1, **i32), out_tokens=torch.zeros(batch, **i32))
@@ -137,7 +138,7 @@ class DecodeEngine:
         from ..ops import records
 
         g = self.geometry
-        span = 64 * (self.world if self.mode == "tp" else 1)
+        span = 64 * self.kv_ranks
         gen = torch.Generator(device=self.device).manual_seed(seed)
         all_ids = []
         for r in range(g.batch):
