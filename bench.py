@@ -62,8 +62,13 @@ def reference_arm(args):
     reason = ("reference installed as pure Python, but its decode path needs SGLang v0.5.22 load_jit + server, DeepGEMM "
               "and FlashMLA (no network to get them) and its Index transport rejects compute capability (10,0): "
               + "; ".join(why))
+    # what CAN be run of the unmodified reference on this box: its kernels, one GPU, through its own loaders
+    kernel_arm = ("python -m ulacache_b200.benchmarks.reference_kernels (reference top-k, index key store and "
+                  "host->HBM exchange compiled from baseline/_ref with tvm_ffi and timed against ours; table in "
+                  "profiles/reference_kernels_vs_ours__same_b200.txt)")
     if int(os.environ.get("RANK", "0")) == 0:            # one line per job, also under torchrun
-        print(json.dumps({"impl": "reference", "unavailable": reason, "n_gpus": args.gpus}))
+        print(json.dumps({"impl": "reference", "unavailable": reason, "kernel_level_arm": kernel_arm,
+                          "n_gpus": args.gpus}))
     return 0
 
 

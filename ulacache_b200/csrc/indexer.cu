@@ -379,7 +379,11 @@ int ulc_index_score_hist(const void* q8, const float* w, const int32_t* page_tab
     const long long ctas = n_q == 1 ? 444 : 296;
     long long per = (total + ctas - 1) / ctas;
     if (per < 8) per = 8;
-    pages_per_cta = static_cast<int>((per + 1) / 2 * 2);
+    per = (per + 1) / 2 * 2;
+    // the grid is R x ceil(max_pages / per): rounding per row must not push it past the resident wave
+    // (four CTAs too many cost a whole second wave)
+    while (static_cast<long long>(R) * ((max_pages + per - 1) / per) > ctas && per < max_pages) per += 2;
+    pages_per_cta = static_cast<int>(per);
   }
   p.pages_per_cta = pages_per_cta + (pages_per_cta & 1);
   dim3 grid((max_pages + p.pages_per_cta - 1) / p.pages_per_cta, R);
