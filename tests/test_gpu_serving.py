@@ -42,3 +42,12 @@ def test_prefill_matches_token_by_token_decode_and_prefix_is_reused(native, monk
     assert rep["finished_requests"] == 2 and rep["reused_prefix_tokens"] == 128 and rep["unserved"] == 0
     assert rep["prefill_tokens"] == 200 + (153 - 128)
     srv_a.close()
+
+
+def test_snapshot_bank_restores_a_cache_that_decodes_the_same_tokens(native, tmp_path):
+    """fill -> save (two owner shards, KV + index planes) -> restore into a fresh engine -> both decode the
+    same tokens over eight steps."""
+    from ulacache_b200.experiments import kv_bank
+
+    assert kv_bank.main(["--tiny", "--layers", "3", "--batch", "3", "--prompt-len", "700", "--steps", "8",
+                         "--dir", str(tmp_path / "bank")]) == 0

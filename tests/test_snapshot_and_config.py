@@ -191,3 +191,59 @@ def test_every_shipped_model_configuration_loads():
             cfg = decode_model_configuration(fh.read())
         adapters.add(cfg.adapter)
     assert {"native", "native_tp", "native_dpa", "dsa", "glm_flash", "paged", "qsa"} <= adapters
+
+
+def test_restore_routing_per_layout():
+    from ulacache_b200.tools.snapshot.bank import restore_routing, shard_positions
+
+    keys = ["a", "b", "c"]
+    dpa = restore_routing(2, keys, world=2, mode="dpa")
+    assert [(s.owner, s.request) for s in dpa[0]] == [(0, "a"), (1, "a"), (0, "c"), (1, "c")]
+    assert [(s.owner, s.request) for s in dpa[1]] == [(0, "b"), (1, "b")] and dpa[1][0].keep == "all"
+    placed = restore_routing(1, keys, world=4, mode="dpa", placement={"a": 3, "b": 3, "c": 0})
+    assert [len(p) for p in placed] == [1, 0, 0, 2]
+    tp = restore_routing(4, keys, world=8, mode="tp")
+    assert all(len(p) == 12 and p[0].keep == "owned" for p in tp)
+    assert restore_routing(4, keys, world=8, mode="tp", kv_layout="replicated")[5][0].keep == "all"
+    assert list(shard_positions(1, 4, 11)) == [1, 5, 9]
+    with pytest.raises(ValueError):
+        restore_routing(1, keys, world=2, mode="dpa", placement={"a": 0, "b": 2, "c": 0})
+
+
+def test_prefix_tree_rebuilt_from_snapshot_requests():
+    from ulacache_b200.serving.radix_tree import RadixPrefixTree
+    from ulacache_b200.tools.snapshot.bank import rebuild_prefix_tree
+    from ulacache_b200.tools.snapshot.format import SnapshotRequest
+
+    shared = list(range(100, 228))                          # two pages of 64 tokens
+    r1 = SnapshotRequest("one", shared + list(range(500, 570)), [7, 8])
+    r2 = SnapshotRequest("two", shared + list(range(900, 964)), [9])
+    tree = RadixPrefixTree()
+    dup = rebuild_prefix_tree(tree, [r1, r2], {"one": [10, 11, 12, 13], "two": [20, 21, 22]})
+    assert dup == {"one": 0, "two": 2}                      # request two's copies of the shared pages are duplicates
+    hit = tree.match(shared + list(range(900, 964)) + [1, 2, 3])
+    assert [n.page for n in hit] == [10, 11, 22]
+    with pytest.raises(ValueError):
+        rebuild_prefix_tree(RadixPrefixTree(), [r1], {"one": [10]})
+
+
+def test_speculative_continuation_round_trip(tmp_path):
+    import torch
+    from ulacache_b200.tools.snapshot.bank import load_continuation, save_continuation
+
+    saved_ids = torch.tensor([640, 641, 642, 643, 704, 705], dtype=torch.int32)      # logical ids of positions 0..5
+    sel = torch.tensor([[705, 640, -1, 642]], dtype=torch.int32)
+    path = tmp_path / "cont.pt"
+    sha = save_continuation(path, hidden_state=torch.randn(1, 16), draft_tokens=torch.tensor([[5, 6, 7]]),
+                            selection_ids=sel, request_ids=saved_ids)
+    restored_ids = torch.tensor([64, 65, 66, 67, 128, 129], dtype=torch.int32)       # the restored run's ids differ
+    out = load_continuation(path, sha, request_ids=restored_ids)
+    assert out["selection_ids"].tolist() == [[129, 64, -1, 66]] and out["draft_tokens"].tolist() == [[5, 6, 7]]
+    assert out["draft_probs"] is None and out["hidden_state"].shape == (1, 16)
+    with pytest.raises(ValueError):
+        load_continuation(path, "0" * 64, request_ids=restored_ids)
+    with pytest.raises(FileExistsError):
+        save_continuation(path, hidden_state=torch.zeros(1, 4))
+    with pytest.raises(ValueError):
+        save_continuation(tmp_path / "bad.pt", hidden_state=torch.zeros(1, 4), selection_ids=torch.tensor([[999]]),
+                          request_ids=saved_ids)

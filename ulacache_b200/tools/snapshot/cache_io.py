@@ -87,3 +87,36 @@ def restore(cache, path: str, request_ids: Dict[str, object], *, verify_payload=
                     data = b"".join(reader.iter_plane(owner, req.key, plane))
                     index_writer(layer, ids, data)
     return done
+
+
+def read_index_records(index_pool_layer, ids, *, page_tokens: int = 64, segment_bytes=(128, 4)):
+    """Index records of logical ids from one layer's index page pool (uint8 [pages, 8448]: per page the
+    keys of its 64 tokens, then their scales) -> uint8 [n, 132] (key bytes then scale bytes per record)."""
+    import torch
+
+    kb, sb = segment_bytes
+    ids = ids.long()
+    page, off = ids // page_tokens, ids % page_tokens
+    cols_k = (off * kb).unsqueeze(1) + torch.arange(kb, device=ids.device)
+    cols_s = (page_tokens * kb + off * sb).unsqueeze(1) + torch.arange(sb, device=ids.device)
+    rows = index_pool_layer[page]
+    return torch.cat([torch.gather(rows, 1, cols_k), torch.gather(rows, 1, cols_s)], dim=1).contiguous()
+
+
+def write_index_records(index_pool_layer, ids, data, *, page_tokens: int = 64, segment_bytes=(128, 4)):
+    """Inverse of :func:`read_index_records`; ``data`` uint8 [n, 132] (or bytes)."""
+    import torch
+
+    kb, sb = segment_bytes
+    if isinstance(data, (bytes, bytearray)):
+        data = torch.frombuffer(bytearray(data), dtype=torch.uint8).view(-1, kb + sb)
+    data = data.to(index_pool_layer.device)
+    ids = ids.long().to(index_pool_layer.device)
+    page, off = ids // page_tokens, ids % page_tokens
+    flat = index_pool_layer.view(-1)
+    width = index_pool_layer.shape[1]
+    base = page * width
+    k_at = (base + off * kb).unsqueeze(1) + torch.arange(kb, device=ids.device)
+    s_at = (base + page_tokens * kb + off * sb).unsqueeze(1) + torch.arange(sb, device=ids.device)
+    flat[k_at.reshape(-1)] = data[:, :kb].reshape(-1)
+    flat[s_at.reshape(-1)] = data[:, kb:].reshape(-1)
