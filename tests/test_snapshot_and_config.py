@@ -247,3 +247,56 @@ def test_speculative_continuation_round_trip(tmp_path):
     with pytest.raises(ValueError):
         save_continuation(tmp_path / "bad.pt", hidden_state=torch.zeros(1, 4), selection_ids=torch.tensor([[999]]),
                           request_ids=saved_ids)
+
+
+def test_pool_adapters_plan_and_build_every_family():
+    """Every shipped configuration that enables the cache becomes a pool plan; a GPU budget cuts the device
+    tier and moves the difference to the host tier; single-owner plans build a working cache on CPU."""
+    import glob
+    import os
+
+    import torch
+    from ulacache_b200.config.model_configuration import load_model_configuration
+    from ulacache_b200.serving.pools import plan_pool
+
+    here = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "ulacache_b200", "config", "models")
+    seen = set()
+    for path in sorted(glob.glob(os.path.join(here, "*.json"))):
+        cfg = load_model_configuration(path)
+        if not cfg.enabled or cfg.device_token_capacity_per_owner is None:
+            continue
+        plan = plan_pool(cfg, layers=4, world=8, max_queries=8)
+        seen.add(plan.adapter)
+        assert plan.device_records % 64 == 0 and plan.gpu_bytes > 0 and plan.bytes["device_records"] > 0
+        tight = plan_pool(cfg, layers=4, world=8, max_queries=8, gpu_budget_bytes=plan.gpu_bytes * 2 // 3)
+        assert tight.device_records < plan.device_records and tight.gpu_bytes <= plan.gpu_bytes * 2 // 3
+        assert tight.device_records + tight.host_records == plan.device_records + plan.host_records
+        if plan.adapter == "glm_flash":
+            assert plan.index_compression_ratio == 4 and plan.index_pages < (plan.device_records + plan.host_records) // 64
+        if plan.adapter == "paged":
+            assert plan.compression_ratios == (1, 2) and len(plan.planes) == 2
+            one = plan_pool(cfg, layers=4, world=8, max_queries=8).bytes["device_records"]
+            assert one == int(plan.device_records * 2 * 1152 * 4 * 1.5)
+    assert {"glm_flash", "paged", "qsa"} <= seen
+    # a budget too small for the fixed charges is refused before anything is allocated
+    cfg = load_model_configuration(os.path.join(here, "qsa-regions-cpu-ngram.json"))
+    with pytest.raises(MemoryError):
+        plan_pool(cfg, layers=2, world=1, gpu_budget_bytes=1 << 16)
+    # single-owner plans of every family build a cache that allocates on CPU
+    import json
+
+    from ulacache_b200.config.model_configuration import decode_model_configuration
+
+    for adapter, opts, engine in (("qsa", {"maximum_write_record_count": 512}, "NativePagedResidency"),
+                                  ("glm_flash", {"prefill_buffer_records": 0}, "UnifiedLocalResidency"),
+                                  ("paged", {"storage_owner_count": 1}, "NativePagedResidency")):
+        small = decode_model_configuration(json.dumps({
+            "schema_version": 1, "adapter": adapter,
+            "capacity": {"device_token_capacity_per_owner": 4096, "host_token_capacity_per_owner": 8192}, "options": opts}))
+        plan = plan_pool(small, layers=2, world=1, max_queries=2, topk=64)
+        assert plan.engine == "local" and plan.owners == 1
+        cache = plan.build("cpu")
+        assert type(cache.engine).__name__ == engine
+        ids = cache.alloc(128)
+        assert ids is not None and ids.numel() == 128
+        cache.free(ids)
