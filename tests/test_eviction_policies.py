@@ -189,3 +189,15 @@ def test_parallel_ring_policy_cpu_semantics():
     assert pol.totals == dict(hits=2, misses=7, evictions=3, overflow=0)
     h, m, ev = pol.step(torch.tensor([20, 21, 22, 23, 24]))            # more misses than evictable slots
     assert m == 5 and len(ev) == 4 and pol.totals["overflow"] == 1
+
+
+def test_sequential_ring_handles_touches_before_the_first_advance():
+    """Slots touched at epoch 0 are victims while recent, turn cold when their bucket is reused at epoch 255 and
+    are evicted first afterwards (host build of the presence-bitmap header)."""
+    import ctypes as C
+
+    from ulacache_b200.ops import _native as N
+
+    lib = N.host()
+    for epochs in (1, 3, 254, 255, 256, 300, 520):
+        assert lib.ulc_presence_ring_epoch0_check(C.c_int(2048), C.c_int(5), C.c_int(epochs)) == 0, epochs

@@ -235,4 +235,41 @@ long long ulc_policy_resident(void* h) {
   return s == nullptr ? -1 : static_cast<long long>(s->slot_of.size());
 }
 
+// Scenario check of the sequential presence ring (ulc/presence_bitmap.h) on the host: `early` slots are
+// touched BEFORE the first advance (epoch 0), one more slot is touched in every later epoch, and the ring is
+// advanced `epochs` times.  The epoch-0 slots must be offered as victims while they are recent (oldest
+// first), move to the cold bucket when their bucket is reused (epoch 255), stay attached, and be the first
+// victims afterwards.  Returns 0, or the number of the first check that failed.
+int ulc_presence_ring_epoch0_check(int slots, int early, int epochs) {
+  if (slots <= 0 || early <= 0 || early + epochs > slots) return -1;
+  std::vector<uint32_t> bits(static_cast<size_t>(ulc::kPresenceBuckets) * ulc::presence_words(slots), 0u);
+  std::vector<int16_t> inverse(slots);
+  auto* ring = new ulc::PresenceRing;
+  ring->init(bits.data(), inverse.data(), slots);
+  int rc = 0;
+  for (int s = 0; s < early; ++s) ring->touch(s);                    // epoch 0, before any advance
+  if (ring->attached() != early) rc = 1;
+  if (!rc && ring->victim() != -1) rc = 2;                           // everything attached is of the current epoch
+  for (int e = 1; e <= epochs && !rc; ++e) {
+    ring->advance();
+    ring->touch(early + e - 1);
+    if (ring->attached() != early + e) { rc = 3; break; }
+    // the epoch-0 slots are the oldest: the victim is the lowest of them, recent or cold
+    if (ring->victim() != 0) { rc = 4; break; }
+    const bool cold = e >= ulc::kPresenceRecent;
+    if (cold && ring->bucket[ulc::kPresenceRecent].count < early) { rc = 5; break; }
+    if (!cold && ring->bucket[ulc::kPresenceRecent].count != 0) { rc = 6; break; }
+  }
+  if (!rc) {                                                         // evict them all: lowest slot first
+    for (int s = 0; s < early; ++s) {
+      const int v = ring->victim();
+      if (v != s) { rc = 7; break; }
+      ring->detach(v);
+    }
+  }
+  if (!rc && epochs >= 2 && ring->victim() != early) rc = 8;         // then the slot of epoch 1 (not current any more)
+  delete ring;
+  return rc;
+}
+
 }  // extern "C"
