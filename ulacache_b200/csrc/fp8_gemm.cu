@@ -489,9 +489,9 @@ fp8_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid
       }
     }
   }
-  if (p.n_peers > 0) __threadfence_system();
   ptx::tc_fence_before();
   __syncthreads();
+  if (p.n_peers > 0 && threadIdx.x == 0) __threadfence_system();      // one cumulative fence per CTA after the barrier
   if (warp == 1) ptx::tmem_dealloc<512>(tmem);
 }
 

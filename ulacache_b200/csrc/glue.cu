@@ -547,7 +547,7 @@ moe_combine_kernel(const __nv_bfloat16* __restrict__ y, const int32_t* __restric
     for (int r = first; r < last && r < peers.n; ++r)
       *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(peers.p[r]) + static_cast<size_t>(drow) * H + c) = ow;
   }
-  if (peers.n > 0) __threadfence_system();
+  if (peers.n > 0) ptx::cta_release_peer_stores();
 }
 
 // Copies up to four local segments to the same offsets of every peer's buffer (the send half
@@ -564,7 +564,7 @@ peer_put_kernel(PutSegs segs, PeerOut peers) {
          i += static_cast<long long>(gridDim.x) * blockDim.x)
       dst[i] = src[i];
   }
-  __threadfence_system();
+  ptx::cta_release_peer_stores();
 }
 
 }  // namespace ulc

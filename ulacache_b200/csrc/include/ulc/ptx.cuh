@@ -228,6 +228,14 @@ __device__ __forceinline__ void st_relaxed_sys_v4(uint4* p, uint4 v) {      // o
                "r"(v.w)
                : "memory");
 }
+// End of a kernel that stored to peer (or host) memory: order ALL of the CTA's stores before whatever a
+// later launch publishes.  The CTA barrier makes every thread's stores happen before thread 0's fence, and
+// a fence is cumulative, so one system-scope fence per CTA does what one per thread would (the pattern of a
+// grid-wide barrier); a fence per thread cost 0.3 to 0.6 ms per decode step in the store-heavy kernels.
+__device__ __forceinline__ void cta_release_peer_stores() {
+  __syncthreads();
+  if (threadIdx.x == 0) __threadfence_system();
+}
 // Wait until *flag >= want.  Gives up after `limit_cycles` and returns false.
 __device__ __forceinline__ bool wait_flag_ge(const int32_t* flag, int32_t want,
                                              long long limit_cycles) {

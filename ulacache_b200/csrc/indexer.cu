@@ -322,7 +322,7 @@ __global__ void candidate_scatter_kernel(const float* __restrict__ vals, const i
     ptx::st_cg16(dv + o, *reinterpret_cast<const uint4*>(vals + e));
     ptx::st_cg16(di + o, *reinterpret_cast<const uint4*>(ids + e));
   }
-  __threadfence_system();
+  ptx::cta_release_peer_stores();
 }
 
 template <int NQ, bool HIST>

@@ -18,6 +18,7 @@
 #include <stdint.h>
 
 #include "ulc/layout.h"
+#include "ulc/ptx.cuh"
 #include "ulc/status.h"
 
 namespace ulc {
@@ -71,7 +72,7 @@ scatter_heads_kernel(const __nv_bfloat16* __restrict__ o, const float* __restric
   for (int i = threadIdx.x; i < units; i += blockDim.x) dst[i] = src[i];
   float* ldst = reinterpret_cast<float*>(lse_dst.p[q]) + row0;
   for (int i = threadIdx.x; i < hs; i += blockDim.x) ldst[i] = lse[static_cast<size_t>(b) * H + q * hs + i];
-  __threadfence_system();
+  ptx::cta_release_peer_stores();
 }
 
 // out[row] = sum_p w_p * part[p][row], w_p = exp(lse_p - max) / sum; part stride = rows_max * hs rows.

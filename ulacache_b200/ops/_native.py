@@ -12,6 +12,7 @@ rejected before launching.
 from __future__ import annotations
 
 import ctypes as C
+import os
 from pathlib import Path
 
 _LIB_DIR = Path(__file__).resolve().parent.parent / "_lib"
