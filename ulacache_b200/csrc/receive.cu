@@ -39,7 +39,10 @@ __global__ void receive_acquire_kernel(ResidencyState st, OwnerMap map, int my_r
     if (atomicAdd(&leases[e], 1) == 0) {
       const int32_t epoch = st.counters[kCntEpoch];
       const int32_t old = atomicExch(&st.stamps[e], kStampLeased);
-      if (old >= 0) atomicSub(&st.ring[bucket_of(old, epoch)], 1);
+      if (old >= 0) {
+        atomicSub(&st.ring[bucket_of(old, epoch)], 1);
+        bm_clear(st, bucket_of(old, epoch), e);
+      }
     }
   }
   locations[i] = e;
@@ -62,6 +65,7 @@ __global__ void receive_release_kernel(ResidencyState st, OwnerMap map, int my_r
     const int32_t epoch = st.counters[kCntEpoch];
     st.stamps[e] = epoch;
     atomicAdd(&st.ring[epoch % kRecentBuckets], 1);
+    bm_set(st, epoch % kRecentBuckets, e);
     st.access_time[local] = epoch;
   }
 }

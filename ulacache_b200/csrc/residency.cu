@@ -12,6 +12,7 @@
 // ulacache/csrc/eviction/victims.cuh:53-194 (victim selection) and the Triton
 // `_remap` kernel (ulacache/cache/kernels/local_cache.py:149).
 #include "ulc/pool.h"
+#include "ulc/presence_ring.h"
 #include "ulc/ptx.cuh"
 #include "ulc/residency.h"
 
@@ -36,6 +37,7 @@ __global__ void register_rows_kernel(ResidencyState st, OwnerMap map, int my_ran
       st.hbm_tags[slot] = local;
       st.stamps[slot] = epoch;
       atomicAdd(&st.ring[epoch % kRecentBuckets], 1);
+      bm_set(st, epoch % kRecentBuckets, slot);
       atomicAdd(&st.counters[kCntRegistered], 1);
       return;
     }
@@ -58,6 +60,7 @@ __global__ void register_rows_kernel(ResidencyState st, OwnerMap map, int my_ran
       st.hbm_tags[slot] = local;
       st.stamps[slot] = epoch;
       atomicAdd(&st.ring[epoch % kRecentBuckets], 1);
+      bm_set(st, epoch % kRecentBuckets, slot);
       atomicAdd(&st.counters[kCntRegistered], 1);
       return;
     }
@@ -79,7 +82,10 @@ __global__ void release_rows_kernel(ResidencyState st, OwnerMap map, int my_rank
   const int32_t epoch = st.counters[kCntEpoch];
   if (dir_on_device(e)) {
     const int32_t stamp = st.stamps[e];
-    if (stamp >= 0) atomicSub(&st.ring[bucket_of(stamp, epoch)], 1);
+    if (stamp >= 0) {
+      atomicSub(&st.ring[bucket_of(stamp, epoch)], 1);
+      bm_clear(st, bucket_of(stamp, epoch), e);
+    }
     st.stamps[e] = -1;
     st.hbm_tags[e] = -1;
     st.hbm_free[atomicAdd(&st.counters[kCntHbmFree], 1)] = e;
@@ -99,6 +105,9 @@ __global__ void begin_step_kernel(ResidencyState st) {
   const int b = epoch % kRecentBuckets;
   st.ring[kColdBucket] += st.ring[b];
   st.ring[b] = 0;
+  // with a bitmap index the bits of the reused bucket (slots last touched 255 epochs ago) move to the
+  // cold bucket in the launch that follows
+  st.counters[kCntRingCtl + kPrDrain] = (st.bits != nullptr && epoch >= kRecentBuckets) ? b : -1;
   st.counters[kCntPromote] = 0;
   st.counters[kCntPlan] = 0;
   st.counters[kCntVictims] = 0;
@@ -122,8 +131,12 @@ __global__ void pin_rows_kernel(ResidencyState st, OwnerMap map, int my_rank,
     if (dir_on_device(e)) {
       const int32_t old = atomicExch(&st.stamps[e], epoch);
       if (old != epoch) {
-        if (old >= 0) atomicSub(&st.ring[bucket_of(old, epoch)], 1);
+        if (old >= 0) {
+          atomicSub(&st.ring[bucket_of(old, epoch)], 1);
+          bm_clear(st, bucket_of(old, epoch), e);
+        }
         atomicAdd(&st.ring[epoch % kRecentBuckets], 1);
+        bm_set(st, epoch % kRecentBuckets, e);
       }
       ++hits;
     } else if (dir_on_host(e)) {
@@ -162,6 +175,29 @@ __global__ void plan_quota_kernel(ResidencyState st, int32_t* status) {
   if (served < want - from_free) {
     report(status, kErrCapacity, want - from_free - served);
     c[kCntUnserved] += want - from_free - served;
+  }
+  if (st.bits != nullptr) {
+    // the same decision as a list of (bucket, take, first output position) for the bitmap emit: the cold
+    // bucket, then recent buckets from the oldest epoch up to the cutoff epoch (which gives `quota`)
+    int listed = 0, got = 0;
+    auto add = [&](int bucket, int take) {
+      if (take <= 0) return;
+      st.vlist[listed * 3] = bucket; st.vlist[listed * 3 + 1] = take; st.vlist[listed * 3 + 2] = got;
+      got += take; ++listed;
+    };
+    if (served > 0) {
+      const int32_t epoch = c[kCntEpoch];
+      if (cutoff == -0x7fffffff) {
+        add(kColdBucket, quota);
+      } else {
+        add(kColdBucket, st.ring[kColdBucket]);
+        for (int32_t e = epoch - kRecentBuckets + 1; e < cutoff && e < epoch; ++e)
+          if (e >= 0) add(e % kRecentBuckets, st.ring[e % kRecentBuckets]);
+        if (cutoff < epoch && cutoff >= 0) add(cutoff % kRecentBuckets, quota);
+      }
+    }
+    c[kCntRingCtl + kPrListed] = listed;
+    c[kCntVictims] = got;
   }
 }
 
@@ -230,7 +266,10 @@ __global__ void commit_kernel(ResidencyState st) {
     const int32_t old_row = st.plan[kPlanOldRow * cap + i];
     if (old_row >= 0) {
       const int32_t old_stamp = st.stamps[gpu];
-      if (old_stamp >= 0) atomicSub(&st.ring[bucket_of(old_stamp, epoch)], 1);
+      if (old_stamp >= 0) {
+        atomicSub(&st.ring[bucket_of(old_stamp, epoch)], 1);
+        bm_clear(st, bucket_of(old_stamp, epoch), gpu);
+      }
       st.directory[old_row] = dir_encode_host(host_dst);
       st.host_tags[host_dst] = old_row;
       atomicAdd(&st.counters[kCntEvictions], 1);
@@ -242,6 +281,7 @@ __global__ void commit_kernel(ResidencyState st) {
     st.hbm_tags[gpu] = row;
     st.stamps[gpu] = epoch;
     atomicAdd(&st.ring[epoch % kRecentBuckets], 1);
+    bm_set(st, epoch % kRecentBuckets, gpu);
     atomicAdd(&st.counters[kCntPromotions], 1);
   }
 }
@@ -304,8 +344,21 @@ int ulc_res_release(const ResidencyState* st, const OwnerMap* map, int my_rank, 
   release_rows_kernel<<<(n + 255) / 256, 256, 0, s>>>(*st, *map, my_rank, ids, n, status);
   return static_cast<int>(cudaGetLastError());
 }
+// The residency state seen as a presence ring (bitmaps, bucket list, control words in the counters).
+static inline PRing ring_view(const ResidencyState* st) {
+  PRing r;
+  r.bits = st->bits; r.summary = st->summary; r.slot_bucket = nullptr; r.count = st->ring; r.bucket_epoch = nullptr;
+  r.ctl = st->counters + kCntRingCtl; r.vlist = st->vlist; r.chunk_count = st->chunk_count;
+  r.n = st->hbm_slots; r.w0 = st->w0; r.w1 = st->w1;
+  return r;
+}
+
 int ulc_res_begin_step(const ResidencyState* st, cudaStream_t s) {
   begin_step_kernel<<<1, 32, 0, s>>>(*st);
+  if (st->bits != nullptr) {
+    const PRing r = ring_view(st);
+    return ulc_pring_drain(&r, 0, s);
+  }
   return static_cast<int>(cudaGetLastError());
 }
 int ulc_res_pin(const ResidencyState* st, const OwnerMap* map, int my_rank, const int32_t* sel, int n,
@@ -318,7 +371,13 @@ int ulc_res_pin(const ResidencyState* st, const OwnerMap* map, int my_rank, cons
 int ulc_res_plan(const ResidencyState* st, int victim_blocks, int assign_blocks, int32_t* status,
                  cudaStream_t s) {
   plan_quota_kernel<<<1, 32, 0, s>>>(*st, status);
-  plan_enumerate_kernel<<<grid_for(st->hbm_slots, 256, victim_blocks > 0 ? victim_blocks : 296), 256, 0, s>>>(*st);
+  if (st->bits != nullptr) {
+    const PRing r = ring_view(st);
+    const int rc = ulc_pring_count_emit(&r, st->victims, st->plan_capacity, s);
+    if (rc != 0) return rc;
+  } else {
+    plan_enumerate_kernel<<<grid_for(st->hbm_slots, 256, victim_blocks > 0 ? victim_blocks : 296), 256, 0, s>>>(*st);
+  }
   plan_assign_kernel<<<grid_for(st->plan_capacity, 256, assign_blocks > 0 ? assign_blocks : 128), 256, 0, s>>>(*st, status);
   return static_cast<int>(cudaGetLastError());
 }

@@ -70,7 +70,10 @@ class ResidencyState(C.Structure):
         "directory", "hbm_tags", "host_tags", "stamps", "access_time", "hbm_free", "host_free",
         "counters", "ring", "promote", "plan", "victims")] + [
         ("dir_len", C.c_int32), ("hbm_slots", C.c_int32), ("host_slots", C.c_int32),
-        ("plan_capacity", C.c_int32)]
+        ("plan_capacity", C.c_int32),
+        # optional presence-bitmap victim index (null pointers = scan the stamps)
+        ("bits", C.c_void_p), ("summary", C.c_void_p), ("vlist", C.c_void_p), ("chunk_count", C.c_void_p),
+        ("w0", C.c_int32), ("w1", C.c_int32)]
 
 
 class PlaneSet(C.Structure):
