@@ -33,7 +33,6 @@ namespace ulc {
 constexpr int kIdxTileTokens = 128;                 // two pages per MMA tile
 constexpr int kIdxStageBytes = kIdxTileTokens * 128; // 16 KB of keys
 constexpr int kIdxStages = 8;
-constexpr int kIdxThreads = 192;                    // producer, MMA, 4 epilogue warps
 constexpr int kIdxMaxQueries = 4;
 constexpr int kIdxBarrierBytes = 768;                   // IdxBarriers: mbarriers + page-table slice
 constexpr int kIdxQBytes = kIdxMaxQueries * 64 * 128;   // 32 KB
@@ -47,11 +46,15 @@ constexpr int kIdxSmem = 1024 + kIdxStages * kIdxStageBytes + kIdxQBytes + kIdxM
 // select kernel needs no pass of its own over the scores to find its threshold bin.
 template <int NQ, bool HIST = false>
 struct IdxGeom {
-  static constexpr int kStages = NQ == 1 ? (HIST ? 3 : 4) : (HIST && NQ == 4 ? 6 : kIdxStages);
+  // One query per request: two epilogue warpgroups take alternate tiles (the epilogue, one thread per key
+  // reading 64 accumulator columns, is the longest stage), two CTAs per SM, five ring stages each.
+  static constexpr int kEpilogueGroups = NQ == 1 ? 2 : 1;
+  static constexpr int kThreads = 64 + 128 * kEpilogueGroups;
+  static constexpr int kStages = NQ == 1 ? 5 : (HIST && NQ == 4 ? 6 : kIdxStages);
   static constexpr int kQBytes = NQ * 64 * 128;
   static constexpr int kHistBytes = HIST ? NQ * kTopkBins * 4 : 0;
   static constexpr int kSmem = 1024 + kStages * kIdxStageBytes + kQBytes + NQ * 64 * 4 + kIdxBarrierBytes + kHistBytes;
-  static constexpr int kCtasPerSm = NQ == 1 ? 3 : 1;
+  static constexpr int kCtasPerSm = NQ == 1 ? 2 : 1;
 };
 
 struct IndexScoreParams {
@@ -90,10 +93,12 @@ __device__ __forceinline__ int local_valid_tokens(int length, int alloc_page, in
 }
 
 template <int NQ, bool HIST>
-__global__ void __launch_bounds__(kIdxThreads, IdxGeom<NQ, HIST>::kCtasPerSm)
+__global__ void __launch_bounds__(IdxGeom<NQ, HIST>::kThreads, IdxGeom<NQ, HIST>::kCtasPerSm)
 index_score_kernel(const __grid_constant__ CUtensorMap tmap_keys, const IndexScoreParams p) {
   constexpr int N = NQ * 64;
   constexpr int kStages = IdxGeom<NQ, HIST>::kStages;
+  constexpr int kIdxThreads = IdxGeom<NQ, HIST>::kThreads;          // (shadows the one-group constant)
+  constexpr int kGroups = IdxGeom<NQ, HIST>::kEpilogueGroups;
   constexpr uint32_t kCols = N * 2 <= 128 ? 128 : N * 2 <= 256 ? 256 : 512;
   extern __shared__ uint8_t idx_smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(idx_smem_raw) + 1023) &
@@ -200,7 +205,8 @@ index_score_kernel(const __grid_constant__ CUtensorMap tmap_keys, const IndexSco
       }
     }
   } else {
-    const int qd = warp & 3;
+    const int qd = warp & 3;                  // TMEM lane quarter this warp may read
+    const int wg = (warp - 2) >> 2;           // epilogue group: takes tiles wg, wg + kGroups, ...
     const int row = qd * 32 + lane;           // token row in the tile
     const int pg_in_tile = row >> 6, off = row & 63;
     const size_t row_stride = static_cast<size_t>(p.max_pages) * kPageTokens;
@@ -218,13 +224,13 @@ index_score_kernel(const __grid_constant__ CUtensorMap tmap_keys, const IndexSco
           : 0.f;
     };
     bool valid_next = false;
-    float kscale_next = fetch_scale(0, valid_next);
-    for (int i = 0; i < ntiles; ++i) {
+    float kscale_next = fetch_scale(wg, valid_next);
+    for (int i = wg; i < ntiles; i += kGroups) {
       const int ab = i & 1;
       const bool valid = valid_next;
       const bool inside = inside_next;
       const float kscale = kscale_next;
-      kscale_next = fetch_scale(i + 1, valid_next);
+      kscale_next = fetch_scale(i + kGroups, valid_next);
       if (*abort_flag || !ptx::mbar_wait(&bar.acc_full[ab], (i >> 1) & 1)) {
         if (!*abort_flag && lane == 0) report(p.status, kErrPipeline, 300 + qd);
         *abort_flag = 1;
@@ -261,9 +267,9 @@ index_score_kernel(const __grid_constant__ CUtensorMap tmap_keys, const IndexSco
     }
     if constexpr (HIST) {
       // the four epilogue warps flush this CTA's non-empty bins into the rows' histograms
-      asm volatile("bar.sync 1, 128;" ::: "memory");
+      asm volatile("bar.sync 1, %0;" ::"n"(128 * kGroups) : "memory");
       const int et = threadIdx.x - 64;
-      for (int i = et; i < NQ * kTopkBins; i += 128) {
+      for (int i = et; i < NQ * kTopkBins; i += 128 * kGroups) {
         const uint32_t c = s_hist[i];
         if (c) atomicAdd(p.topk_ws + static_cast<size_t>(r * NQ + i / kTopkBins) * (kTopkWsRowBytes / 4) + (i % kTopkBins), c);
       }
@@ -331,7 +337,7 @@ static int launch_index_score(const CUtensorMap& tm, const IndexScoreParams& p, 
   const int rc = ensure_dynamic_smem(reinterpret_cast<const void*>(index_score_kernel<NQ, HIST>),
                                      IdxGeom<NQ, HIST>::kSmem, once);
   if (rc != 0) return rc;
-  index_score_kernel<NQ, HIST><<<grid, kIdxThreads, IdxGeom<NQ, HIST>::kSmem, s>>>(tm, p);
+  index_score_kernel<NQ, HIST><<<grid, IdxGeom<NQ, HIST>::kThreads, IdxGeom<NQ, HIST>::kSmem, s>>>(tm, p);
   return static_cast<int>(cudaGetLastError());
 }
 
@@ -373,10 +379,10 @@ int ulc_index_score_hist(const void* q8, const float* w, const int32_t* page_tab
   p.R = R; p.n_q = n_q; p.max_pages = max_pages; p.ranks = ranks; p.rank = rank;
   p.pages_per_rank = pages_per_rank;
   if (pages_per_cta <= 0) {
-    // one resident wave: 148 SMs x 3 CTAs (one query per request) or two waves of one CTA per SM;
+    // one resident wave: 148 SMs x 2 CTAs (one query per request) or two waves of one CTA per SM;
     // at least 8 pages (4 tiles) each
     const long long total = static_cast<long long>(R) * max_pages;
-    const long long ctas = n_q == 1 ? 444 : 296;
+    const long long ctas = 296;
     long long per = (total + ctas - 1) / ctas;
     if (per < 8) per = 8;
     per = (per + 1) / 2 * 2;

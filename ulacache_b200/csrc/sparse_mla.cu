@@ -533,22 +533,29 @@ sparse_mla_decode_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gri
 }
 
 // Merge KV splits: out = sum_s w_s * O_s with w_s = exp(lse_s - max) / sum.
-// One CTA per (query, head) row; a thread owns 4 consecutive output dims and keeps four splits'
-// 16-byte loads in flight.  A split whose LSE is -inf saw no token and its partial O is not read.
-__global__ void mla_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_lse,
-                                   __nv_bfloat16* __restrict__ out, float* __restrict__ lse, int rows,
-                                   int splits) {
-  const int row = blockIdx.x;
+// One WARP per (query, head) row: lane s reads split s's log-sum-exp once and the weights travel by
+// shuffle; a lane owns 16 output dims and has every split's 16-byte loads of a step in flight before it
+// uses one (two dependent memory round trips per row instead of four).  A split whose LSE is -inf saw no
+// token and its partial O is not read.
+constexpr int kCombineWarps = 8;
+__global__ void __launch_bounds__(kCombineWarps * 32)
+mla_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_lse,
+                   __nv_bfloat16* __restrict__ out, float* __restrict__ lse, int rows, int splits) {
+  const int lane = threadIdx.x & 31;
+  const int row = blockIdx.x * kCombineWarps + (threadIdx.x >> 5);
   if (row >= rows) return;
-  float m = -INFINITY;
-  for (int s = 0; s < splits; ++s) m = fmaxf(m, part_lse[static_cast<size_t>(s) * rows + row]);
-  float denom = 0.f;
-  for (int s = 0; s < splits; ++s) {
-    const float v = part_lse[static_cast<size_t>(s) * rows + row];
-    denom += v > -INFINITY ? expf(v - m) : 0.f;
-  }
+  const float mine = lane < splits ? part_lse[static_cast<size_t>(lane) * rows + row] : -INFINITY;
+  float m = mine;
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+  const float wgt = mine > -INFINITY ? expf(mine - m) : 0.f;
+  float denom = wgt;
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) denom += __shfl_xor_sync(0xffffffffu, denom, o);
   const float inv = denom > 0.f ? 1.f / denom : 0.f;
-  for (int d = threadIdx.x * 4; d < 512; d += blockDim.x * 4) {
+#pragma unroll
+  for (int step = 0; step < 4; ++step) {
+    const int d = step * 128 + lane * 4;
     float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
     for (int s0 = 0; s0 < splits; s0 += 4) {
       float4 v[4];
@@ -556,9 +563,9 @@ __global__ void mla_combine_kernel(const float* __restrict__ part_o, const float
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
         const int s = s0 + j;
-        const float l = s < splits ? part_lse[static_cast<size_t>(s) * rows + row] : -INFINITY;
-        w[j] = l > -INFINITY ? expf(l - m) : 0.f;
-        v[j] = l > -INFINITY
+        w[j] = __shfl_sync(0xffffffffu, wgt, s & 31);
+        if (s >= splits) w[j] = 0.f;
+        v[j] = w[j] > 0.f
                    ? *reinterpret_cast<const float4*>(part_o + (static_cast<size_t>(s) * rows + row) * 512 + d)
                    : make_float4(0.f, 0.f, 0.f, 0.f);
       }
@@ -577,7 +584,7 @@ __global__ void mla_combine_kernel(const float* __restrict__ part_o, const float
     ow.y = *reinterpret_cast<const uint32_t*>(&o1);
     *reinterpret_cast<uint2*>(out + static_cast<size_t>(row) * 512 + d) = ow;
   }
-  if (lse && threadIdx.x == 0) lse[row] = denom > 0.f ? m + logf(denom) : -INFINITY;
+  if (lse && lane == 0) lse[row] = denom > 0.f ? m + logf(denom) : -INFINITY;
 }
 
 // 3-D map over a query tensor addressed as [query b][head h][dim]: box = 64 dims x 64 heads.
@@ -655,7 +662,8 @@ int ulc_sparse_mla_decode_ex(const PoolView* pv, const void* q_lat, long long la
   r = static_cast<int>(cudaGetLastError());
   if (r != 0) return r;
   if (splits > 1) {
-    mla_combine_kernel<<<B * H, 128, 0, stream>>>(p.part_o, p.part_lse, p.out, lse, B * H, splits);
+    mla_combine_kernel<<<(B * H + kCombineWarps - 1) / kCombineWarps, kCombineWarps * 32, 0, stream>>>(
+        p.part_o, p.part_lse, p.out, lse, B * H, splits);
     r = static_cast<int>(cudaGetLastError());
   }
   return r;
@@ -668,7 +676,9 @@ int ulc_merge_partial_attention(const float* part_o, const float* part_lse, void
                                 int parts, cudaStream_t stream) {
   if (rows <= 0 || parts <= 0) return 0;
   if ((reinterpret_cast<uintptr_t>(part_o) & 15) || (reinterpret_cast<uintptr_t>(out) & 7)) return -kErrAlignment;
-  mla_combine_kernel<<<rows, 128, 0, stream>>>(part_o, part_lse, reinterpret_cast<__nv_bfloat16*>(out), lse, rows, parts);
+  if (parts > 32) return -kErrUnsupported;
+  mla_combine_kernel<<<(rows + kCombineWarps - 1) / kCombineWarps, kCombineWarps * 32, 0, stream>>>(
+      part_o, part_lse, reinterpret_cast<__nv_bfloat16*>(out), lse, rows, parts);
   return static_cast<int>(cudaGetLastError());
 }
 
