@@ -137,3 +137,22 @@ def test_parallel_presence_ring_matches_its_cpu_twin_step_by_step(native):
     assert int(ring.count.sum()) == capacity - gpu.nfree
     pop = sum(bin(int(w) & 0xffffffff).count("1") for w in ring.bits.cpu().flatten().tolist())
     assert pop == capacity - gpu.nfree
+
+
+def test_captured_decode_trace_replays_through_the_device_policies(native, tmp_path):
+    """Selections of a running engine -> device trace ring -> file -> replay through every device policy."""
+    from ulacache_b200.experiments import scheduler_study as S
+    from ulacache_b200.telemetry import load_trace, validate_trace_coverage
+
+    path = str(tmp_path / "trace.npy")
+    n = S.capture_decode_trace(path, steps=5, batch=3, prompt_len=600, layers=2, tiny=True)
+    assert n == 5 * 2 * 3 * 128                                   # steps x layers x requests x top-k
+    trace = load_trace(path)
+    assert validate_trace_coverage(trace, 5, 2) == []
+    steps = [ids for ids, _ in S.trace_from_file(path)]
+    rows = S.gpu_policy_timing(steps, 256, max(max(s) for s in steps) + 1)
+    by = {r["policy"]: r for r in rows}
+    assert set(by) == {"exact_lru", "linked_list", "presence_ring_one_thread", "presence_ring_parallel"}
+    assert all(r["median_us_per_step"] > 0 and 0.0 <= r["hit_rate"] <= 1.0 for r in rows)
+    # pinning every hit before choosing victims can only help: no more misses than the in-order ring
+    assert by["presence_ring_parallel"]["hit_rate"] >= by["presence_ring_one_thread"]["hit_rate"] - 1e-9

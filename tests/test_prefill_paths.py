@@ -90,3 +90,60 @@ def test_packed_regions_expand_and_remap_cpu():
     assert toks[1].tolist()[8:] == [-4, -3, -2, -1]                     # beyond the row's count
     out = remap_packed_regions(packed, torch.tensor([[40, -1, 0], [36, 28, 4]]), lay)
     assert out[0].tolist() == [(10 << 32) | 17, -1, -1] and out[1].tolist() == [(9 << 32) | 1, (7 << 32) | 2, (1 << 32) | 9]
+
+
+def _offload_scenario(device):
+    """Write 256 records into a cache whose HBM tier holds them all, offload half to the host tier, and
+    read everything back through the access path (which promotes what the selection needs)."""
+    import ulacache_b200 as ula
+    from ulacache_b200.bindings import LocalCacheBindings
+    from ulacache_b200.ops import records
+    from helpers import make_spec, random_kv
+
+    cache = ula.init(make_spec(layers=2, device_pages=6, host_pages=8, queries=2, topk=128), LocalCacheBindings(device=device))
+    ids = cache.alloc(256)
+    latent, rope = random_kv(256, 3)
+    latent, rope = latent.to(device), rope.to(device)
+    for layer in range(2):
+        cache.write(ids, layer, (latent * (layer + 1), rope))
+    res = cache.engine.residency[0]
+    assert bool((res.directory[ids.long()] >= 0).all())                   # everything starts in HBM
+    moved = ids[64:192]
+    cache.engine.offload_prefill(moved)
+    entry = res.directory[ids.long()].cpu()
+    out = {"on_host": int((entry[64:192] <= -2).sum()), "still_device": int((entry >= 0).sum())}
+    got = {}
+    for k, part in enumerate((ids[:128], ids[128:])):            # one access per layer and forward
+        cache.begin_model_forward()
+        for layer in range(2):
+            cache.access(part.view(1, -1).to(torch.int32), layer)
+            got[(layer, k)] = cache.gather_selected_records(layer).clone().cpu().view(-1, 656)
+            cache.finish_layer_attention(layer)
+        cache.finish_model_forward()
+    cache.check()
+    # the byte-exact reference is what the cache held before the offload: re-encode on the same device path
+    fresh = ula.init(make_spec(layers=2, device_pages=6, host_pages=8, queries=2, topk=128), LocalCacheBindings(device=device))
+    ids2 = fresh.alloc(256)
+    for layer in range(2):
+        fresh.write(ids2, layer, (latent * (layer + 1), rope))
+    want = {}
+    for k, part in enumerate((ids2[:128], ids2[128:])):
+        fresh.begin_model_forward()
+        for layer in range(2):
+            fresh.access(part.view(1, -1).to(torch.int32), layer)
+            want[(layer, k)] = fresh.gather_selected_records(layer).clone().cpu().view(-1, 656)
+            fresh.finish_layer_attention(layer)
+        fresh.finish_model_forward()
+    out["bytes_equal"] = all(torch.equal(got[key], want[key]) for key in want)
+    return out
+
+
+def test_offload_prefill_rows_cpu():
+    out = _offload_scenario("cpu")
+    assert out == {"on_host": 128, "still_device": 128, "bytes_equal": True}
+
+
+@pytest.mark.gpu
+def test_offload_prefill_rows_with_the_copy_kernel(native):
+    out = _offload_scenario("cuda")
+    assert out == {"on_host": 128, "still_device": 128, "bytes_equal": True}
