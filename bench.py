@@ -207,8 +207,9 @@ def main():
     from ulacache_b200.ops import _native as N
     from ulacache_b200.serving.engine import DecodeEngine, init_distributed
 
-    if os.environ.get("NCCL_DEBUG", "").upper() in ("", "VERSION"):
-        os.environ["NCCL_DEBUG"] = "WARN"          # keep NCCL's version banner off stdout: one JSON line only
+    # whatever NCCL logs (its version banner at the VERSION and WARN levels, more at INFO) goes to stderr:
+    # stdout carries the result line only
+    os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")
     rank, world, local, group, cpu_group = init_distributed()
     if world != args.gpus:
         raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE is {world}")

@@ -64,3 +64,31 @@ def test_sparse_mla_lens_and_bf16_records(native):
     assert torch.allclose(out.float(), ref_o, atol=2e-2)
     assert torch.isinf(lse[2]).all() and (out[2] == 0).all()
     assert torch.allclose(lse[:2], ref_l[:2], atol=2e-2)
+
+
+def test_cta_pair_launch_matches_independent_ctas(native):
+    """The two-CTA cluster variant (each CTA gathers half of every tile into both) gives the results of
+    the default launch, with masked tokens, KV splits and both record formats' common path."""
+    from ulacache_b200.ops import sparse_mla as M
+
+    torch.manual_seed(7)
+    slots = 8192
+    pool = _pool(slots)
+    view, keep = _view(pool)
+    status = N.new_status("cuda")
+    for B, K, splits in ((3, 2048, 2), (2, 700, 1), (1, 64, 1)):
+        q = (torch.randn(B, 128, 576, device="cuda") * 0.5).to(torch.bfloat16)
+        loc = torch.stack([torch.randperm(slots, device="cuda")[:K] for _ in range(B)]).to(torch.int32)
+        loc[torch.rand(B, K, device="cuda") < 0.15] = -1
+        outs = []
+        for pair in (False, True):
+            M.set_pair_launch(pair)
+            try:
+                o, lse = M.sparse_mla_decode(view, q, loc, 576 ** -0.5, splits=splits, status=status)
+                torch.cuda.synchronize()
+            finally:
+                M.set_pair_launch(False)
+            N.raise_on_status(status, "sparse_mla pair")
+            outs.append((o.float(), lse))
+        assert torch.allclose(outs[0][0], outs[1][0], atol=2e-3, rtol=2e-2)
+        assert torch.allclose(outs[0][1], outs[1][1], atol=1e-3, rtol=1e-3)

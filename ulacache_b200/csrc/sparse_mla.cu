@@ -20,6 +20,20 @@
 // S is two 64x64 partial accumulators (even / odd 64-dim slabs of the contraction,
 // one per MMA-issuing thread) per buffer at columns [256,512).
 //
+// CTA pair (template PAIR, used when the head blocks come in twos): the two CTAs that serve the two
+// head blocks of one (query, KV split) need the SAME K tiles.  They run as a cluster of two; each CTA's
+// producer warps gather and dequantise HALF of every tile (32 records) and store it into BOTH CTAs'
+// shared memory (distributed shared memory), so the scattered record reads - the stage that bounds the
+// tile rate - are halved per SM and every record crosses NVLink / HBM once instead of twice.  A stage's
+// "full" barrier counts the producer warps of both CTAs; its "free" barrier counts the MMA issuers of
+// both (their commits are delivered to both CTAs), since either CTA's producers write into both.
+// Measured (one B200, 32 queries x 128 heads x 2048 records): 73.4 us per layer against 68.3 us for
+// independent CTAs, and 116.6 against 108.5 us for the owner-side attention of the two-rank micro-benchmark.
+// Halving the gather per SM does not shorten a tile, so the gather rate is not what bounds it: the period
+// is set by the dependent chain store -> QK^T -> softmax -> PV of which two stages are in flight, and the
+// pair adds distributed-shared-memory stores and cluster-scope barriers to that chain.  OFF by default
+// (ulc_sparse_mla_set_pair / ULC_MLA_PAIR=1 switch it on).
+//
 // The reference library has no attention kernel (it hands rows to FlashMLA) and
 // moves remote rows with record_pull_cached_impl
 // (ulacache/csrc/cache/common.cuh:1037) into a local buffer first; this kernel
@@ -74,6 +88,7 @@ struct MlaBarriers {
   uint32_t tmem_base;
   int abort_flag;
   uint32_t mask[kMlaStages][2];   // valid-token bits of the tile in each stage
+  uint8_t mask_pair[kMlaStages][16];   // PAIR: 4 valid bits per producer warp of the pair (CTA rank * 8 + warp)
 };
 
 // Optional per-tile timeline of CTA (0,0,0), compiled in with -DULC_MLA_TRACE (development only):
@@ -125,6 +140,7 @@ __device__ __forceinline__ void dequant16(const uint4& in, float scale, uint4& l
   hi = make_uint4(o[4], o[5], o[6], o[7]);
 }
 
+template <bool PAIR>
 __global__ void __launch_bounds__(kMlaThreads, 1)
 sparse_mla_decode_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_qr,
                          const MlaParams p) {
@@ -141,6 +157,7 @@ sparse_mla_decode_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gri
   const int b = blockIdx.y;            // query
   const int split = blockIdx.z;
   const int h0 = hb * kMlaM;
+  const uint32_t crank = PAIR ? ptx::cluster_ctarank() : 0u;      // which half of every tile this CTA gathers
 
   // token range of this CTA, in whole tiles
   int n_valid = p.lens ? min(max(p.lens[b], 0), p.K) : p.K;
@@ -152,8 +169,8 @@ sparse_mla_decode_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gri
   if (threadIdx.x == 0) {
     ptx::mbar_init(&bar.qfull, 1);
     for (int s = 0; s < kMlaStages; ++s) {
-      ptx::mbar_init(&bar.kfull[s], kProducerWarps);
-      ptx::mbar_init(&bar.kfree[s], kMmaIssuers);
+      ptx::mbar_init(&bar.kfull[s], PAIR ? 2 * kProducerWarps : kProducerWarps);
+      ptx::mbar_init(&bar.kfree[s], PAIR ? 2 * kMmaIssuers : kMmaIssuers);
       ptx::mbar_init(&bar.sfull[s], kMmaIssuers);
       ptx::mbar_init(&bar.pready[s], kSoftmaxWarps);
     }
@@ -169,6 +186,7 @@ sparse_mla_decode_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gri
   }
   ptx::tc_fence_before();
   __syncthreads();
+  if constexpr (PAIR) ptx::cluster_sync_all();      // the peer's barriers exist before anyone arrives on them
   ptx::tc_fence_after();
   const uint32_t tmem = bar.tmem_base;
   volatile int* abort_flag = &bar.abort_flag;
@@ -211,7 +229,16 @@ sparse_mla_decode_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gri
           sv[j] = keep + __shfl_xor_sync(0xffffffffu, give, 16);
         }
       }
-      const uint32_t mask = bar.mask[st][half];
+      uint32_t mask;
+      if constexpr (PAIR) {
+        // tokens [32 half, 32 half + 32) were gathered by CTA `half` of the pair: 4 bits per producer warp
+        const uint64_t nib = *reinterpret_cast<const volatile uint64_t*>(&bar.mask_pair[st][half * 8]);
+        mask = 0;
+#pragma unroll
+        for (int w = 0; w < 8; ++w) mask |= static_cast<uint32_t>((nib >> (8 * w)) & 0xfu) << (4 * w);
+      } else {
+        mask = bar.mask[st][half];
+      }
       float mx = -INFINITY;
 #pragma unroll
       for (int j = 0; j < 32; ++j) {
@@ -398,7 +425,8 @@ sparse_mla_decode_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gri
         for (int kk = 0; kk < 4; ++kk)
           ptx::umma_bf16(d, ptx::umma_desc_advance(p_desc, kk * 32), ptx::umma_desc_advance(v_desc, kk * 2048),
                          idesc_pv, (i | kk) != 0);
-        ptx::umma_commit(&bar.kfree[st]);
+        if constexpr (PAIR) ptx::umma_commit_mc(&bar.kfree[st], 0x3);     // the stage is free in BOTH CTAs' eyes
+        else ptx::umma_commit(&bar.kfree[st]);
         ptx::umma_commit(&bar.odone);
         if (me == 0) MLA_T(1, i, 3);             // PV issued
       };
@@ -414,7 +442,8 @@ sparse_mla_decode_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gri
           issue_pv(pv_next++);
           idle_since = 0;
         } else if (qk_next < ntiles && qk_next <= pv_next + 1 &&
-                   ptx::mbar_test_wait(&bar.kfull[qk_next & 1], (qk_next >> 1) & 1)) {
+                   (PAIR ? ptx::mbar_test_wait_cluster(&bar.kfull[qk_next & 1], (qk_next >> 1) & 1)
+                         : ptx::mbar_test_wait(&bar.kfull[qk_next & 1], (qk_next >> 1) & 1))) {
           issue_qk(qk_next++);
           idle_since = 0;
         } else {
@@ -437,9 +466,15 @@ sparse_mla_decode_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gri
     // conversion and the MMAs of the previous one.  (Measured: the tile rate is bound by how many
     // scattered sector reads one SM keeps in flight through L1, about 9 B/clk, not by the math.)
     const int pw = warp - kSoftmaxWarps - kMmaIssuers;   // 0..7
-    const int tt = lane & 7;                     // token within the warp's group
-    const int part = lane >> 3;                  // 0..3: which chunks of the record
-    const int trow = pw * 8 + tt;                // row in the tile
+    // alone: 8 tokens per warp, a lane owns a quarter of a record; pair: 4 tokens per warp out of this CTA's
+    // 32, a lane owns an eighth of a record
+    constexpr int kParts = PAIR ? 8 : 4;         // lanes per record
+    constexpr int kLat = 32 / kParts;            // latent chunks (16 B) per lane
+    constexpr int kRope = 8 / kParts;            // rotary chunks per lane
+    const int tt = PAIR ? (lane & 3) : (lane & 7);       // token within the warp's group
+    const int part = PAIR ? (lane >> 2) : (lane >> 3);   // which chunks of the record
+    const int trow = PAIR ? static_cast<int>(crank) * 32 + pw * 4 + tt : pw * 8 + tt;   // row in the tile
+    const uint32_t peer = crank ^ 1u;
     struct Regs { uint4 lat[8]; uint4 rope[2]; uint4 sc; const uint8_t* rec; };
     // Locations are read two tiles before the records they name, so that a fetch never
     // waits on the location load before it can issue its record loads.
@@ -462,57 +497,81 @@ sparse_mla_decode_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gri
       r.sc = make_uint4(0, 0, 0, 0);
       if (p.format == 0) {
 #pragma unroll
-        for (int j = 0; j < 8; ++j) r.lat[j] = r.rec ? ptx::ld_nc16(r.rec + (part + 4 * j) * 16) : make_uint4(0, 0, 0, 0);
+        for (int j = 0; j < kLat; ++j)
+          r.lat[j] = r.rec ? ptx::ld_nc16(r.rec + (part + kParts * j) * 16) : make_uint4(0, 0, 0, 0);
         if (r.rec) r.sc = ptx::ld_nc16(r.rec + kRec656ScaleOffset);
 #pragma unroll
-        for (int j = 0; j < 2; ++j)
-          r.rope[j] = r.rec ? ptx::ld_nc16(r.rec + kRec656RopeOffset + (part + 4 * j) * 16) : make_uint4(0, 0, 0, 0);
+        for (int j = 0; j < kRope; ++j)
+          r.rope[j] = r.rec ? ptx::ld_nc16(r.rec + kRec656RopeOffset + (part + kParts * j) * 16) : make_uint4(0, 0, 0, 0);
       }
     };
     auto store = [&](int i, const Regs& r) -> bool {
       const int st = i & 1;
-      if (*abort_flag || !ptx::mbar_wait(&bar.kfree[st], ((i >> 1) & 1) ^ 1)) {
+      if (*abort_flag || !(PAIR ? ptx::mbar_wait_cluster(&bar.kfree[st], ((i >> 1) & 1) ^ 1)
+                                : ptx::mbar_wait(&bar.kfree[st], ((i >> 1) & 1) ^ 1))) {
         if (!*abort_flag && lane == 0) report(p.status, kErrPipeline, 7000 + i);
         *abort_flag = 1;
         return false;
       }
       uint8_t* kt = sk + st * kKBytes;
+      // one 16-byte chunk into the tile of this CTA and, in a pair, of the peer CTA as well
+      auto put = [&](uint8_t* dst, const uint4& v) {
+        *reinterpret_cast<uint4*>(dst) = v;
+        if constexpr (PAIR) ptx::st_cluster16(ptx::mapa(ptx::smem_u32(dst), peer), v);
+      };
       if (pw == 0 && lane == 0) MLA_T(2, i, 1);  // stage free
       if (p.format == 0) {
         const float scales[4] = {__uint_as_float(r.sc.x), __uint_as_float(r.sc.y), __uint_as_float(r.sc.z),
                                  __uint_as_float(r.sc.w)};
 #pragma unroll
-        for (int j = 0; j < 8; ++j) {
-          const int ch = part + 4 * j;           // 16-value chunk 0..31 of the latent
+        for (int j = 0; j < kLat; ++j) {
+          const int ch = part + kParts * j;      // 16-value chunk 0..31 of the latent
           uint4 lo, hi;
           dequant16(r.lat[j], scales[ch >> 3], lo, hi);
           uint8_t* slab = kt + (ch >> 2) * kSlab;
-          *reinterpret_cast<uint4*>(slab + ptx::sw128_offset(trow, (ch & 3) * 2)) = lo;
-          *reinterpret_cast<uint4*>(slab + ptx::sw128_offset(trow, (ch & 3) * 2 + 1)) = hi;
+          put(slab + ptx::sw128_offset(trow, (ch & 3) * 2), lo);
+          put(slab + ptx::sw128_offset(trow, (ch & 3) * 2 + 1), hi);
         }
 #pragma unroll
-        for (int j = 0; j < 2; ++j)
-          *reinterpret_cast<uint4*>(kt + 8 * kSlab + ptx::sw128_offset(trow, part + 4 * j)) = r.rope[j];
+        for (int j = 0; j < kRope; ++j)
+          put(kt + 8 * kSlab + ptx::sw128_offset(trow, part + kParts * j), r.rope[j]);
       } else {
         // 576 bf16 = 72 chunks: latent chunks 0..63 then rotary 64..71; 18 per lane
+        constexpr int kPer = 72 / kParts;        // chunks per lane: 18 alone, 9 in a pair
+        constexpr int kStep = kPer / 3;
 #pragma unroll 1
-        for (int j0 = 0; j0 < 18; j0 += 6) {
-          uint4 v[6];
+        for (int j0 = 0; j0 < kPer; j0 += kStep) {
+          uint4 v[kStep];
 #pragma unroll
-          for (int j = 0; j < 6; ++j)
-            v[j] = r.rec ? ptx::ld_nc16(r.rec + (part + 4 * (j0 + j)) * 16) : make_uint4(0, 0, 0, 0);
+          for (int j = 0; j < kStep; ++j)
+            v[j] = r.rec ? ptx::ld_nc16(r.rec + (part + kParts * (j0 + j)) * 16) : make_uint4(0, 0, 0, 0);
 #pragma unroll
-          for (int j = 0; j < 6; ++j) {
-            const int ch = part + 4 * (j0 + j);
-            *reinterpret_cast<uint4*>(kt + (ch >> 3) * kSlab + ptx::sw128_offset(trow, ch & 7)) = v[j];
+          for (int j = 0; j < kStep; ++j) {
+            const int ch = part + kParts * (j0 + j);
+            put(kt + (ch >> 3) * kSlab + ptx::sw128_offset(trow, ch & 7), v[j]);
           }
         }
       }
-      const uint32_t bits = __ballot_sync(0xffffffffu, r.rec != nullptr) & 0xffu;
-      if (lane == 0) reinterpret_cast<volatile uint8_t*>(&bar.mask[st][0])[pw] = static_cast<uint8_t>(bits);
-      ptx::fence_async_smem();
-      __syncwarp();
-      if (lane == 0) ptx::mbar_arrive(&bar.kfull[st]);
+      if constexpr (PAIR) {
+        const uint32_t bits = __ballot_sync(0xffffffffu, r.rec != nullptr) & 0xfu;
+        if (lane == 0) {
+          uint8_t* cell = &bar.mask_pair[st][crank * 8 + pw];
+          *reinterpret_cast<volatile uint8_t*>(cell) = static_cast<uint8_t>(bits);
+          ptx::st_cluster_u8(ptx::mapa(ptx::smem_u32(cell), peer), bits);
+        }
+        ptx::fence_async_all();                 // both CTAs' tensor cores read what this warp stored
+        __syncwarp();
+        if (lane == 0) {
+          ptx::mbar_arrive_cluster(ptx::mapa(ptx::smem_u32(&bar.kfull[st]), crank));
+          ptx::mbar_arrive_cluster(ptx::mapa(ptx::smem_u32(&bar.kfull[st]), peer));
+        }
+      } else {
+        const uint32_t bits = __ballot_sync(0xffffffffu, r.rec != nullptr) & 0xffu;
+        if (lane == 0) reinterpret_cast<volatile uint8_t*>(&bar.mask[st][0])[pw] = static_cast<uint8_t>(bits);
+        ptx::fence_async_smem();
+        __syncwarp();
+        if (lane == 0) ptx::mbar_arrive(&bar.kfull[st]);
+      }
       if (pw == 0 && lane == 0) MLA_T(2, i, 2);  // tile published
       if (lane == 0) MLA_T(3, i, pw);            // ... by each producer warp
       return true;
@@ -529,6 +588,9 @@ sparse_mla_decode_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gri
   }
   ptx::tc_fence_before();
   __syncthreads();
+  // neither CTA of a pair may leave while the other can still store into its shared memory or arrive on
+  // its barriers (every wait above is bounded, so both get here even after a failure)
+  if constexpr (PAIR) ptx::cluster_sync_all();
   if (warp == kSoftmaxWarps) ptx::tmem_dealloc<kTmemCols>(tmem);
 }
 
@@ -614,6 +676,10 @@ int ulc_mla_trace_read(long long* host) {
 }
 #endif
 
+// CTA-pair launch (see the file comment): off unless switched on, it measured slower.
+static int g_mla_pair = 0;
+void ulc_sparse_mla_set_pair(int on) { g_mla_pair = on ? 1 : 0; }
+
 long long ulc_sparse_mla_scratch_bytes(int B, int H, int splits) {
   if (splits <= 1) return 0;
   return static_cast<long long>(splits) * B * H * (512 + 1) * 4;
@@ -637,8 +703,10 @@ int ulc_sparse_mla_decode_ex(const PoolView* pv, const void* q_lat, long long la
   if (splits > 1 && scratch == nullptr) return -kErrUnsupported;
   if (splits > 1 && (out_sb != static_cast<long long>(H) * 512 || out_sh != 512)) return -kErrUnsupported;
   if ((out_sb & 7) || (out_sh & 7) || (reinterpret_cast<uintptr_t>(out) & 15)) return -kErrAlignment;
-  static PerDeviceOnce once;
-  const int attr_rc = ensure_dynamic_smem(reinterpret_cast<const void*>(sparse_mla_decode_kernel), kMlaSmem, once);
+  static PerDeviceOnce once, once_pair;
+  int attr_rc = ensure_dynamic_smem(reinterpret_cast<const void*>(sparse_mla_decode_kernel<false>), kMlaSmem, once);
+  if (attr_rc != 0) return attr_rc;
+  attr_rc = ensure_dynamic_smem(reinterpret_cast<const void*>(sparse_mla_decode_kernel<true>), kMlaSmem, once_pair);
   if (attr_rc != 0) return attr_rc;
   CUtensorMap tq, tr;
   int r = make_q_tmap(&tq, q_lat, B, H, 512, lat_sb, lat_sh);
@@ -658,8 +726,25 @@ int ulc_sparse_mla_decode_ex(const PoolView* pv, const void* q_lat, long long la
   p.scale_log2 = sm_scale * 1.4426950408889634f;
   p.format = format;
   dim3 grid((H + kMlaM - 1) / kMlaM, B, splits);
-  sparse_mla_decode_kernel<<<grid, kMlaThreads, kMlaSmem, stream>>>(tq, tr, p);
-  r = static_cast<int>(cudaGetLastError());
+  if (g_mla_pair && grid.x % 2 == 0) {
+    // the two head blocks of a (query, split) as a cluster of two CTAs sharing every K tile
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = dim3(kMlaThreads);
+    cfg.dynamicSmemBytes = kMlaSmem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    r = static_cast<int>(cudaLaunchKernelEx(&cfg, sparse_mla_decode_kernel<true>, tq, tr, p));
+  } else {
+    sparse_mla_decode_kernel<false><<<grid, kMlaThreads, kMlaSmem, stream>>>(tq, tr, p);
+    r = static_cast<int>(cudaGetLastError());
+  }
   if (r != 0) return r;
   if (splits > 1) {
     mla_combine_kernel<<<(B * H + kCombineWarps - 1) / kCombineWarps, kCombineWarps * 32, 0, stream>>>(

@@ -31,8 +31,9 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--layers", type=int, default=0, help="fewer layers for a quick look (not a valid benchmark)")
     args = ap.parse_args()
-    if os.environ.get("NCCL_DEBUG", "").upper() in ("", "VERSION"):
-        os.environ["NCCL_DEBUG"] = "WARN"
+    # whatever NCCL logs (its version banner at the VERSION and WARN levels, more at INFO) goes to stderr:
+    # stdout carries the result line only
+    os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")
     sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__)))))
     from bench import pick_unique_layers
 

@@ -44,6 +44,26 @@ def sparse_mla_reference(q, planes, loc, sm_scale, *, decode=records.decode_scal
     return out, lse
 
 
+def set_pair_launch(on: bool):
+    """``True``: the two head blocks of a (query, KV split) run as a cluster of two CTAs that share every K
+    tile (each gathers half of it into both CTAs' shared memory).  Measured 7 % slower than independent
+    CTAs (the default), see ``csrc/sparse_mla.cu``; kept for comparisons (``ULC_MLA_PAIR=1``)."""
+    N.cuda().ulc_sparse_mla_set_pair(C.c_int(int(on)))
+
+
+_pair_env_applied = False
+
+
+def _apply_pair_env():
+    global _pair_env_applied
+    if not _pair_env_applied:
+        import os
+
+        _pair_env_applied = True
+        if os.environ.get("ULC_MLA_PAIR", "0") == "1":
+            set_pair_launch(True)
+
+
 def default_splits(B: int, H: int, K: int, sm_count: int = 148) -> int:
     """KV splits so that at least one wave of CTAs exists at small batch."""
     ctas = B * ((H + 63) // 64)
@@ -65,6 +85,7 @@ def sparse_mla_decode(pool_view, q, loc, sm_scale, *, lens=None, splits=0, fmt_c
 
     assert q.is_cuda and q.dtype == torch.bfloat16 and q.is_contiguous() and q.shape[-1] == 576
     assert loc.dtype == torch.int32 and loc.stride(1) == 1
+    _apply_pair_env()
     B, H, _ = q.shape
     K = loc.shape[1]
     if splits <= 0:
@@ -108,6 +129,7 @@ def sparse_mla_decode_strided_auto(pool_view, q_lat, q_rope, loc, sm_scale, *, f
     Returns (out bf16 [B,H,512], lse fp32 [B,H])."""
     import torch
 
+    _apply_pair_env()
     B, H, _ = q_lat.shape
     K = loc.shape[1]
     if splits <= 0:

@@ -111,8 +111,9 @@ def main(argv=None):
     from ..models.dsa_moe import DsaMoeConfig
     from .engine import DecodeEngine, init_distributed
 
-    if os.environ.get("NCCL_DEBUG", "").upper() in ("", "VERSION"):
-        os.environ["NCCL_DEBUG"] = "WARN"
+    # whatever NCCL logs (its version banner at the VERSION and WARN levels, more at INFO) goes to stderr:
+    # stdout carries the result line only
+    os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")
     sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__)))))
     from bench import pick_unique_layers
 
