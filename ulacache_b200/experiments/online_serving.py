@@ -130,26 +130,71 @@ def main():
                         median_input=args.median_input, sigma=args.sigma, input_cap=args.input_cap, out_lo=ol, out_hi=oh,
                         rate=args.rate, vocab=cfg.vocab)
     longest = max(len(r["prompt"]) + r["max_new"] for r in trace)
-    srv = ServingEngine(cfg, max_batch=args.max_batch, max_context=longest + 64, device_records=args.device_records,
-                        host_records=int(args.device_records * args.host_multiple), prefill_chunk=args.prefill_chunk)
+    import os
     import time
 
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank, group, cpu_group = 0, None, None
+    device = None
+    if world > 1:
+        # one process per GPU: every rank builds the same trace and serves the sessions dealt to it
+        from ..serving.engine import init_distributed
+
+        rank, world, local, group, cpu_group = init_distributed()
+        device = torch.device("cuda", local)
+        torch.cuda.set_device(device)
+    srv = ServingEngine(cfg, max_batch=args.max_batch, max_context=longest + 64, device_records=args.device_records,
+                        host_records=int(args.device_records * args.host_multiple), prefill_chunk=args.prefill_chunk,
+                        device=device, rank=rank, world=world, group=group, cpu_group=cpu_group)
+    mine = [r for r in trace if r["session"] % world == rank]
+    if world > 1:
+        import torch.distributed as dist
+
+        dist.barrier(group=cpu_group)
     t0 = time.perf_counter()
     srv.clock = lambda: time.perf_counter() - t0
-    for r in trace:
+    for r in mine:
         srv.submit(r["rid"], r["prompt"], r["max_new"], r["arrival"])
     steps = 0
-    while srv.busy():
-        if srv.step() == "idle":
+    while True:
+        state = srv.step()
+        if state == "done":
+            break
+        if state == "idle":
             time.sleep(0.001)
         steps += 1
     torch.cuda.synchronize()
     rep = srv.report()
+    if world > 1:
+        # percentiles over every rank's finished requests; counters summed
+        fin = [r for r in srv.finished if r.first_token_time is not None]
+        local_stats = dict(ttft=[r.first_token_time - r.arrival for r in fin],
+                           tpot=[(r.finish_time - r.first_token_time) / max(1, len(r.generated) - 1) for r in fin if len(r.generated) > 1],
+                           out_tokens=sum(len(r.generated) for r in fin), last_finish=max((r.finish_time for r in fin), default=0.0),
+                           report=rep)
+        every = [None] * world
+        dist.all_gather_object(every, local_stats, group=cpu_group)
+        from ..serving.server import percentile
+
+        ttft_all = [t for e in every for t in e["ttft"]]
+        tpot_all = [t for e in every for t in e["tpot"]]
+        wall = max(e["last_finish"] for e in every) or 1e-9
+        rep = {k: sum(e["report"][k] for e in every) for k in
+               ("admitted_requests", "finished_requests", "rejected_requests", "prefill_tokens", "reused_prefix_tokens",
+                "cached_prefix_pages", "kv_token_capacity", "promotions", "evictions", "unserved")}
+        rep.update(ttft_s_p50=percentile(ttft_all, 50), ttft_s_p99=percentile(ttft_all, 99),
+                   tpot_s_p50=percentile(tpot_all, 50), tpot_s_p99=percentile(tpot_all, 99),
+                   output_tokens_per_s=sum(e["out_tokens"] for e in every) / wall,
+                   decode_steps=max(e["report"]["decode_steps"] for e in every), ranks=world,
+                   padding_steps_rank0=srv.stats.get("padding_steps", 0))
     rep.update(experiment="online_serving", requests=len(trace), sessions=args.sessions, layers=cfg.layers,
                device_records=args.device_records, host_records=int(args.device_records * args.host_multiple),
                total_prompt_tokens=sum(len(r["prompt"]) for r in trace), engine_steps=steps)
-    print(json.dumps(rep))
+    if rank == 0:
+        print(json.dumps(rep))
     srv.close()
+    if world > 1:
+        dist.destroy_process_group()
 
 
 if __name__ == "__main__":

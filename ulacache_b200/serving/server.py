@@ -1,5 +1,6 @@
-"""Continuous-batching server loop around the model and the tiered cache (one GPU; the multi-GPU
-decode layouts are driven by :class:`~ulacache_b200.serving.engine.DecodeEngine`).
+"""Continuous-batching server loop around the model and the tiered cache, on one GPU or on several in
+the data-parallel-attention layout (one process per GPU, requests dealt to the ranks; every rank keeps
+its own cache, radix tree and scheduler and the ranks meet in the expert layers).
 
     srv = ServingEngine(cfg, max_batch=32, max_context=16384, device_records=..., host_records=...)
     srv.submit(request_id, prompt_token_ids, max_new_tokens, arrival_time)
@@ -13,6 +14,11 @@ KV and index key are written before any row is scored).  Finished prompts leave 
 the radix tree; a later request with the same prefix starts from them.  Admission charges a
 request's whole history against ``device + host`` records; the cache decides which tier a record
 lives in and promotes what sparse attention selects.
+
+Several ranks: the expert exchange needs every rank in every layer with the same number of rows, so
+the ranks agree on each step's row count over the CPU group (one small all-gather per step: a prefill
+chunk anywhere makes it a ``prefill_chunk``-row step, otherwise ``max_batch`` rows) and fill up with
+padding rows that write into a scratch page nobody reads.  The loop ends when no rank has work left.
 
 Reference: the serving behaviour the reference gets from SGLang plus its adapters
 (patches/sglang.patch:2144-2322 allocator, :8662-8836 admission, scripts/7_1_online/run.py metrics).
@@ -53,7 +59,8 @@ def percentile(values, p):
 
 class ServingEngine:
     def __init__(self, cfg, *, max_batch: int, max_context: int, device_records: int, host_records: int = 0,
-                 prefill_chunk: int = 512, device=None, seed: int = 0, clock=time.perf_counter):
+                 prefill_chunk: int = 512, device=None, seed: int = 0, clock=time.perf_counter,
+                 rank: int = 0, world: int = 1, group=None, cpu_group=None):
         import torch
         from .. import client
         from ..bindings import LocalCacheBindings
@@ -66,6 +73,7 @@ class ServingEngine:
         self.cfg, self.clock = cfg, clock
         self.device = torch.device(device or "cuda")
         self.max_batch, self.chunk = max_batch, prefill_chunk
+        self.rank, self.world, self.cpu_group = rank, world, cpu_group
         rows = max(max_batch, prefill_chunk)
         device_records = device_records // 64 * 64
         host_records = host_records // 64 * 64
@@ -80,8 +88,14 @@ class ServingEngine:
         self.cache = client.init(spec, LocalCacheBindings(device=self.device))
         total_pages = (device_records + host_records) // PAGE_TOKENS
         self.index_pool = torch.zeros((cfg.layers, total_pages + 2, 8448), dtype=torch.uint8, device=self.device)
-        self.model = DsaMoeModel(cfg, device=self.device, cache=self.cache, index_pool=self.index_pool, tp=1, rank=0,
-                                 max_batch=rows, max_context=max_context + 8, seed=seed)
+        self.model = DsaMoeModel(cfg, device=self.device, cache=self.cache, index_pool=self.index_pool, tp=world, rank=rank,
+                                 group=group, cpu_group=cpu_group, mode="dpa", max_batch=rows,
+                                 max_context=max_context + 8, seed=seed)
+        self._pad_page = None
+        if world > 1:
+            # padding rows of a step write their key / record into this page (position 0) and attend to it
+            ids = self.cache.alloc(PAGE_TOKENS)
+            self._pad_page = int(ids[0]) // PAGE_TOKENS
         self.admission = AdmissionController(CacheBudget(owners=1, device_records=device_records,
                                                          host_records=host_records, max_running_requests=max_batch))
         self.tree = RadixPrefixTree()
@@ -102,7 +116,25 @@ class ServingEngine:
         return True
 
     def busy(self) -> bool:
+        """Work left on THIS rank (several ranks: keep calling ``step`` until it returns "done")."""
         return bool(self.waiting or self.prefilling or self.running)
+
+    def _agree(self, want_rows: int, prefill: bool):
+        """Several ranks: (rows every rank runs this step, whether any rank still has work)."""
+        if self.world == 1:
+            return want_rows, self.busy()
+        import torch
+        import torch.distributed as dist
+
+        mine = torch.tensor([want_rows, int(prefill), int(self.busy())], dtype=torch.int64)
+        every = [torch.zeros(3, dtype=torch.int64) for _ in range(self.world)]
+        dist.all_gather(every, mine, group=self.cpu_group)
+        every = torch.stack(every)
+        if int(every[:, 2].sum()) == 0:
+            return 0, False
+        if int(every[:, 0].max()) == 0:
+            return 0, True                                        # everybody is waiting for arrivals
+        return (self.chunk if int(every[:, 1].max()) else self.max_batch), True
 
     def _alloc_pages(self, n: int) -> Optional[List[int]]:
         import torch
@@ -153,6 +185,7 @@ class ServingEngine:
         i32 = dict(dtype=torch.int32, device=self.device)
         tokens = torch.tensor([t for _, t, _ in rows], **i32)
         lengths = torch.tensor([p for _, _, p in rows], **i32)
+        pad = getattr(self, "_pad_rows", 0)
         # one page-table row per distinct request, expanded to its rows (a prefill chunk is thousands of
         # rows of one request)
         order, index = {}, []
@@ -165,8 +198,15 @@ class ServingEngine:
             if k not in seen:
                 seen.add(k)
                 table[k, : len(r.pages)] = torch.tensor(r.pages, dtype=torch.int32)
-        pages = table.to(self.device)[torch.tensor(index, device=self.device)]
-        return DecodeBatch(tokens=tokens, lengths=lengths, req_pages=pages, out_tokens=torch.zeros(len(rows), **i32))
+        pages = table.to(self.device)[torch.tensor(index, device=self.device)] if rows else \
+            torch.full((0, self.max_pages), -1, **i32)
+        if pad:
+            tokens = torch.cat([tokens, torch.zeros(pad, **i32)])
+            lengths = torch.cat([lengths, torch.zeros(pad, **i32)])
+            extra = torch.full((pad, self.max_pages), -1, **i32)
+            extra[:, 0] = self._pad_page
+            pages = torch.cat([pages, extra])
+        return DecodeBatch(tokens=tokens, lengths=lengths, req_pages=pages, out_tokens=torch.zeros(tokens.numel(), **i32))
 
     def step(self):
         import torch
@@ -175,17 +215,35 @@ class ServingEngine:
         if self._start is None:
             self._start = now
         self._admit(now)
+        # what this rank wants to run
+        plan, rows = "idle", []
         if self.prefilling:
             r = self.prefilling[0]
             lo = r.done_prompt
             hi = min(len(r.prompt), lo + self.chunk)
-            batch = self._batch([(r, r.prompt[p], p) for p in range(lo, hi)])
-            out = self.model.decode_step(batch)
-            self.stats["prefill_tokens"] += hi - lo
+            plan, rows = "prefill", [(r, r.prompt[p], p) for p in range(lo, hi)]
+        elif self.running:
+            plan, rows = "decode", [(r, r.generated[-1], len(r.prompt) + len(r.generated) - 1) for r in self.running]
+        step_rows, anyone = self._agree(len(rows), plan == "prefill")
+        if not anyone:
+            return "done"
+        if step_rows == 0:
+            return "idle"
+        if self.world > 1 and len(rows) > step_rows:
+            # (a decode batch is at most max_batch rows and a chunk at most prefill_chunk; a prefill step
+            # holds both, a decode step only the former)
+            raise RuntimeError("the agreed step is smaller than this rank's rows")
+        self._pad_rows = step_rows - len(rows) if self.world > 1 else 0
+        out = self.model.decode_step(self._batch(rows))
+        self._pad_rows = 0
+        if plan == "prefill":
+            r = self.prefilling[0]
+            hi = r.done_prompt + len(rows)
+            self.stats["prefill_tokens"] += len(rows)
             self.stats["prefill_steps"] += 1
             r.done_prompt = hi
             if hi == len(r.prompt):
-                tok = int(out[-1])                                # sample of the last prompt position
+                tok = int(out[len(rows) - 1])                     # sample of the last prompt position
                 torch.cuda.synchronize()
                 r.first_token_time = self.clock()
                 r.generated.append(tok)
@@ -195,13 +253,12 @@ class ServingEngine:
                 else:
                     self._retire(r)
             return "prefill"
-        if self.running:
-            rows = [(r, r.generated[-1], len(r.prompt) + len(r.generated) - 1) for r in self.running]
-            out = self.model.decode_step(self._batch(rows)).tolist()
+        if plan == "decode":
+            toks = out[: len(rows)].tolist()
             self.stats["decode_steps"] += 1
             self.stats["decoded_tokens"] += len(rows)
             t = None
-            for r, tok in zip(list(self.running), out):
+            for r, tok in zip(list(self.running), toks):
                 r.generated.append(int(tok))
                 if len(r.generated) >= r.max_new:
                     if t is None:
@@ -211,9 +268,8 @@ class ServingEngine:
                     self.running.remove(r)
                     self._retire(r)
             return "decode"
-        if self.waiting:
-            return "idle"
-        return "done"
+        self.stats["padding_steps"] = self.stats.get("padding_steps", 0) + 1
+        return "padding"                                          # only other ranks had rows
 
     def _retire(self, r: _Request):
         import torch
@@ -251,4 +307,7 @@ class ServingEngine:
                 "promotions": c.get("promotions", 0), "evictions": c.get("evictions", 0), "unserved": c.get("unserved", 0)}
 
     def close(self):
+        heap = getattr(self.model, "comm_heap", None)
+        if heap is not None:
+            heap.close()
         self.cache.close()
