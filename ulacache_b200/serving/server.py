@@ -7,8 +7,8 @@ its own cache, radix tree and scheduler and the ranks meet in the expert layers)
     while srv.busy(): srv.step()
     srv.report()          # admitted requests, TTFT / TPOT percentiles, tokens/s, prefix reuse, tier traffic
 
-One ``step`` either prefills one chunk of one request or decodes one token for every running
-request.  Prefill reuses the decode kernels: the chunk's tokens are rows of a batch that all point at
+One ``step`` decodes one token for every running request and, in the rows a prefill-sized step has
+left, prefills the next chunk of one admitted request (decode never waits for a prompt).  Prefill reuses the decode kernels: the chunk's tokens are rows of a batch that all point at
 the same request pages, with per-row context lengths (causal inside the chunk because every row's
 KV and index key are written before any row is scored).  Finished prompts leave their whole pages in
 the radix tree; a later request with the same prefix starts from them.  Admission charges a
@@ -215,31 +215,44 @@ class ServingEngine:
         if self._start is None:
             self._start = now
         self._admit(now)
-        # what this rank wants to run
-        plan, rows = "idle", []
+        # what this rank wants to run: one token for every running request, and - in the room a prefill-sized
+        # step leaves beside them - the next chunk of the request being prefilled (decode never waits for a prompt)
+        dec = [(r, r.generated[-1], len(r.prompt) + len(r.generated) - 1) for r in self.running]
+        pre = []
         if self.prefilling:
             r = self.prefilling[0]
             lo = r.done_prompt
-            hi = min(len(r.prompt), lo + self.chunk)
-            plan, rows = "prefill", [(r, r.prompt[p], p) for p in range(lo, hi)]
-        elif self.running:
-            plan, rows = "decode", [(r, r.generated[-1], len(r.prompt) + len(r.generated) - 1) for r in self.running]
-        step_rows, anyone = self._agree(len(rows), plan == "prefill")
+            hi = min(len(r.prompt), lo + max(0, self.chunk - len(dec)))
+            pre = [(r, r.prompt[p], p) for p in range(lo, hi)]
+        rows = dec + pre
+        step_rows, anyone = self._agree(len(rows), bool(pre))
         if not anyone:
             return "done"
         if step_rows == 0:
             return "idle"
         if self.world > 1 and len(rows) > step_rows:
-            # (a decode batch is at most max_batch rows and a chunk at most prefill_chunk; a prefill step
-            # holds both, a decode step only the former)
             raise RuntimeError("the agreed step is smaller than this rank's rows")
         self._pad_rows = step_rows - len(rows) if self.world > 1 else 0
         out = self.model.decode_step(self._batch(rows))
         self._pad_rows = 0
-        if plan == "prefill":
+        t = None
+        if dec:
+            toks = out[: len(dec)].tolist()
+            self.stats["decode_steps"] += 1
+            self.stats["decoded_tokens"] += len(dec)
+            for (r, _, _), tok in zip(dec, toks):
+                r.generated.append(int(tok))
+                if len(r.generated) >= r.max_new:
+                    if t is None:
+                        torch.cuda.synchronize()
+                        t = self.clock()
+                    r.finish_time = t
+                    self.running.remove(r)
+                    self._retire(r)
+        if pre:
             r = self.prefilling[0]
-            hi = r.done_prompt + len(rows)
-            self.stats["prefill_tokens"] += len(rows)
+            hi = r.done_prompt + len(pre)
+            self.stats["prefill_tokens"] += len(pre)
             self.stats["prefill_steps"] += 1
             r.done_prompt = hi
             if hi == len(r.prompt):
@@ -253,20 +266,7 @@ class ServingEngine:
                 else:
                     self._retire(r)
             return "prefill"
-        if plan == "decode":
-            toks = out[: len(rows)].tolist()
-            self.stats["decode_steps"] += 1
-            self.stats["decoded_tokens"] += len(rows)
-            t = None
-            for r, tok in zip(list(self.running), toks):
-                r.generated.append(int(tok))
-                if len(r.generated) >= r.max_new:
-                    if t is None:
-                        torch.cuda.synchronize()
-                        t = self.clock()
-                    r.finish_time = t
-                    self.running.remove(r)
-                    self._retire(r)
+        if dec:
             return "decode"
         self.stats["padding_steps"] = self.stats.get("padding_steps", 0) + 1
         return "padding"                                          # only other ranks had rows
