@@ -52,7 +52,8 @@ def test_dense_fp8_gemm(native, M, Nout, K, splits):
     assert err <= 0.01 * ref.abs().max().item() + 1e-2, err
 
 
-def test_grouped_fp8_gemm_ragged_experts(native):
+def test_grouped_fp8_gemm_ragged_experts(native, monkeypatch):
+    monkeypatch.setenv("ULC_PREFILL_GEMM", "0")        # the weight-stationary kernel at every ring geometry
     torch.manual_seed(3)
     E, Nout, K = 12, 256, 1024
     counts = torch.tensor([0, 3, 17, 1, 0, 130, 16, 64, 2, 0, 300, 5])
@@ -87,8 +88,9 @@ def test_grouped_fp8_gemm_ragged_experts(native):
 
 
 @pytest.mark.parametrize("M", [32, 48, 256])
-def test_dense_fp8_gemm_long_k(native, M):
+def test_dense_fp8_gemm_long_k(native, M, monkeypatch):
     """Many K blocks per tile (the ring wraps several times) for each ring geometry."""
+    monkeypatch.setenv("ULC_PREFILL_GEMM", "0")
     torch.manual_seed(M)
     Nout, K = 512, 7168
     x = torch.randn(M, K, device="cuda", dtype=torch.bfloat16)
@@ -147,3 +149,60 @@ def test_dense_split_k_reduced_in_the_kernel(native, M, Nout, K, splits):
     torch.cuda.synchronize()
     N.raise_on_status(status, "fp8 gemm")
     assert torch.equal(bufs[0], y) and torch.equal(bufs[1], y)
+
+
+@pytest.mark.parametrize("M,Nout,K", [(130, 128, 128), (256, 256, 512), (300, 384, 1024), (1100, 512, 7168),
+                                      (2048, 2304, 2048)])
+def test_token_major_gemm_dense(native, M, Nout, K):
+    """Prefill-sized rows: tokens on the TMEM lanes, one block scale per thread and K block; partial last row tile,
+    more items than CTAs, K rings that wrap."""
+    torch.manual_seed(M + K)
+    x = torch.randn(M, K, device="cuda", dtype=torch.bfloat16)
+    w = torch.randn(Nout, K, device="cuda") * 0.05
+    x8, sx = fp8.act_quant(x)
+    w8, sw = fp8.quantize_weight(w)
+    status = N.new_status("cuda")
+    y = fp8.many_rows_gemm(x8, sx, fp8.tile_weight(w8), sw, status=status)
+    torch.cuda.synchronize()
+    N.raise_on_status(status, "token-major fp8 gemm")
+    ref = fp8.grouped_gemm_reference(x8, sx, w8, sw)
+    err = (y.float() - ref).abs().max().item()
+    assert err <= 0.01 * ref.abs().max().item() + 1e-2, err
+    if fp8.many_rows(M, 1):        # the public entry takes the same kernel from these sizes on
+        y2 = fp8.grouped_gemm(x8, sx, fp8.tile_weight(w8), sw, status=status)
+        torch.cuda.synchronize()
+        assert torch.equal(y, y2)
+
+
+def test_token_major_gemm_ragged_experts(native):
+    """Experts with no rows, a few rows, exactly one tile, several tiles; rows behind the last expert stay untouched."""
+    torch.manual_seed(5)
+    E, Nout, K = 12, 384, 1024
+    counts = torch.tensor([0, 3, 128, 1, 0, 130, 16, 64, 257, 0, 300, 5])
+    offs = torch.zeros(E + 1, dtype=torch.int32)
+    offs[1:] = counts.cumsum(0)
+    used = int(offs[-1])
+    M = used + 40
+    x = torch.randn(M, K, device="cuda", dtype=torch.bfloat16)
+    w = torch.randn(E, Nout, K, device="cuda") * 0.05
+    x8, sx = fp8.act_quant(x)
+    w8, sw = fp8.quantize_weight(w)
+    status = N.new_status("cuda")
+    out = torch.full((M, Nout), 7.0, device="cuda", dtype=torch.bfloat16)
+    y = fp8.many_rows_gemm(x8, sx, fp8.tile_weight(w8), sw, offs.cuda(), out=out, status=status)
+    torch.cuda.synchronize()
+    N.raise_on_status(status, "token-major grouped fp8 gemm")
+    ref = fp8.grouped_gemm_reference(x8[:used], sx[:used], w8, sw, offs)
+    err = (y[:used].float() - ref).abs().max().item()
+    assert err <= 0.01 * ref.abs().max().item() + 1e-2, err
+    assert (y[used:] == 7.0).all()
+    # against the weight-stationary kernel on the same operands
+    import os
+    os.environ["ULC_PREFILL_GEMM"] = "0"
+    try:
+        y0 = fp8.grouped_gemm(x8[:used].contiguous(), sx[:used].contiguous(), fp8.tile_weight(w8), sw, offs.cuda(),
+                              status=status)
+    finally:
+        os.environ.pop("ULC_PREFILL_GEMM")
+    torch.cuda.synchronize()
+    assert (y[:used].float() - y0.float()).abs().max().item() <= 0.01 * ref.abs().max().item() + 1e-2

@@ -45,6 +45,57 @@ def dense_sweep(args):
         del ws
 
 
+def prefill_sweep(args):
+    """The GEMMs of one decoder layer at prefill chunk sizes (``--rows`` tokens): the token-major kernel against
+    the weight-stationary decode kernel; TFLOP/s of device time (inputs and weights exceed L2 for the MoE cases,
+    the dense weights rotate over copies)."""
+    import torch
+    from ..ops import fp8
+
+    dev = "cuda"
+    peaks = measured_peaks()
+    M = args.rows
+    cases = [("w_in", 1, 2304, 7168, M), ("w_qb", 1, 32768, 1536, M), ("w_o", 1, 7168, 16384, M),
+             ("moe_w13", 256, 4096, 7168, 8 * M), ("moe_w2", 256, 7168, 2048, 8 * M)]
+    if args.small:
+        cases = [("w_in", 1, 2304, 7168, M), ("moe_w13", 32, 4096, 7168, 8 * M)]
+    for name, E, Nout, K, rows in cases:
+        copies = 1 if E > 1 else 3
+        ws = [fp8.random_fp8_weight((E, Nout, K) if E > 1 else (Nout, K), device=dev) for _ in range(copies)]
+        x8, sx = fp8.act_quant(torch.randn(rows, K, device=dev, dtype=torch.bfloat16))
+        offs = None
+        if E > 1:                      # uniform routing: rows / E per expert, the remainder on the first experts
+            counts = torch.full((E,), rows // E, dtype=torch.int64)
+            counts[: rows % E] += 1
+            offs = torch.zeros(E + 1, dtype=torch.int32)
+            offs[1:] = counts.cumsum(0)
+            offs = offs.to(dev)
+        out = torch.empty((rows, Nout), dtype=torch.bfloat16, device=dev)
+        i = [0]
+
+        def token_major():
+            q, s = ws[i[0] % copies]
+            i[0] += 1
+            fp8.many_rows_gemm(x8, sx, q, s, offs, out=out)
+
+        def stationary():
+            import os
+
+            q, s = ws[i[0] % copies]
+            i[0] += 1
+            os.environ["ULC_PREFILL_GEMM"] = "0"
+            fp8.grouped_gemm(x8, sx, q, s, offs, out=out, max_rows=128)
+            os.environ["ULC_PREFILL_GEMM"] = "1"
+
+        flops = 2.0 * rows * Nout * K
+        for label, fn in (("token_major", token_major), ("weight_stationary", stationary)):
+            us = time_cuda(fn, iters=args.iters, warmup=3)
+            emit(kernel="fp8_gemm_prefill", arm=label, case=f"{name} E={E} {Nout}x{K}", rows=rows, us=round(us, 1),
+                 tflops=round(flops / us / 1e6, 1), weight_gb_per_s=round(E * Nout * K / us / 1e3, 1),
+                 frac_of_bf16_peak=round(flops / us / 1e6 / peaks["bf16_tflops"], 3))
+        del ws
+
+
 def main():
     import torch
     from ..ops import fp8
@@ -54,9 +105,14 @@ def main():
     ap.add_argument("--iters", type=int, default=10)
     ap.add_argument("--dense-sweep", action="store_true",
                     help="the dense projections of one decoder layer at 32 and 64 rows: every K split and ring geometry")
+    ap.add_argument("--prefill", action="store_true",
+                    help="one layer's GEMMs at a prefill chunk of --rows tokens: token-major against weight-stationary")
+    ap.add_argument("--rows", type=int, default=2048)
     args = ap.parse_args()
     if args.dense_sweep:
         return dense_sweep(args)
+    if args.prefill:
+        return prefill_sweep(args)
     dev = "cuda"
     peaks = measured_peaks()
     torch.manual_seed(0)

@@ -171,6 +171,10 @@ def grouped_gemm(x8, sx, w8, sw, offs=None, *, splits=1, out=None, status=None, 
     e, nout, k = w8.shape[0], w8.shape[1] * 128, w8.shape[2] * 128
     m = x8.shape[0]
     assert x8.is_contiguous() and w8.is_contiguous() and sx.is_contiguous() and sw.is_contiguous()
+    if not peer_out and many_rows(m, e, max_rows):
+        if out is None:
+            out = torch.empty((m, nout), dtype=torch.bfloat16, device=x8.device)
+        return many_rows_gemm(x8, sx, w8, sw, offs, out=out, status=status)
     if splits > 1 and e == 1 and _splitk_fits(m, nout, splits, max_rows):
         # dense layer at decode size: K splits reduced inside the kernel (no cleared fp32 buffer, no
         # atomics, no conversion launch); the result may also go straight to peers
@@ -218,6 +222,46 @@ def grouped_gemm(x8, sx, w8, sw, offs=None, *, splits=1, out=None, status=None, 
         if out is None:
             return acc.to(torch.bfloat16)
         out.copy_(acc)
+    return out
+
+
+MANY_ROWS_DENSE = 512          # token rows from which a dense layer takes the token-major kernel
+MANY_ROWS_PER_EXPERT = 32      # expected rows per expert from which a grouped layer does
+
+
+def many_rows(m: int, experts: int, max_rows: int = 0) -> bool:
+    """Whether a GEMM of ``m`` token rows over ``experts`` weight sets is prefill-sized: the weight-stationary
+    decode kernel re-streams every weight tile once per 128 rows and pays a column-scaled epilogue; from these
+    sizes on the token-major kernel (``csrc/fp8_prefill_gemm.cu``) wins.  ``m`` of a grouped layer counts every
+    allocated row (other ranks' experts included), so the caller's expected rows per expert (``max_rows``, the ring
+    geometry hint: 64 means more than 24 expected) decides when given.  ``ULC_PREFILL_GEMM=0`` switches it off."""
+    import os
+
+    if os.environ.get("ULC_PREFILL_GEMM", "1") == "0" or m < 256:
+        return False
+    if experts == 1:
+        return m >= MANY_ROWS_DENSE
+    if max_rows > 0:
+        return max_rows >= 64
+    return m >= MANY_ROWS_PER_EXPERT * experts
+
+
+def many_rows_gemm(x8, sx, w8, sw, offs=None, *, out=None, status=None):
+    """Token-major block-scaled fp8 GEMM (tokens on the TMEM lanes, one scale per thread and K block).  Same
+    operands as ``grouped_gemm``; ``w8`` [E, Nout/128, K/128, 128, 128].  Returns bf16 [M, Nout]."""
+    import torch
+
+    if w8.dim() == 4:
+        w8, sw = w8.unsqueeze(0), sw.unsqueeze(0)
+    e, nout, k = w8.shape[0], w8.shape[1] * 128, w8.shape[2] * 128
+    m = x8.shape[0]
+    if out is None:
+        out = torch.empty((m, nout), dtype=torch.bfloat16, device=x8.device)
+    assert out.is_contiguous() and out.shape == (m, nout)
+    N.check(N.cuda().ulc_fp8_prefill_gemm(
+        N.ptr(x8), N.ptr(sx), N.ptr(w8), N.ptr(sw), N.ptr(offs),
+        C.c_int(m), C.c_int(nout), C.c_int(k), C.c_int(e), C.c_int((m + 127) // 128 + e), N.ptr(out), N.ptr(status),
+        N.stream()), "fp8_prefill_gemm")
     return out
 
 
