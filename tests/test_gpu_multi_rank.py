@@ -41,3 +41,19 @@ def test_two_rank_serving_replay_finishes_every_request():
     assert out["ranks"] == 2 and out["finished_requests"] == out["requests"] and out["rejected_requests"] == 0
     assert out["reused_prefix_tokens"] > 0 and out["unserved"] == 0
     assert out["ttft_s_p50"] > 0 and out["output_tokens_per_s"] > 0
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_a_departed_rank_is_seen_on_the_host_before_the_next_launch():
+    """A rank leaves between steps with nothing in flight; the other learns of it from the heartbeats before its
+    next launch, launches nothing towards it, and its own GPU keeps working.  Plain peer stores, no multicast."""
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+    repo = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    res = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2",
+                          "--master-addr", "127.0.0.1", "--master-port", "29691", "-m",
+                          "ulacache_b200.benchmarks.rank_departure_check"], cwd=repo, env=env, capture_output=True,
+                         text=True, timeout=300)
+    assert res.returncode == 0, res.stdout[-2000:] + res.stderr[-4000:]
+    out = json.loads([l for l in res.stdout.splitlines() if l.startswith("{")][-1])
+    assert out["steps_before_departure_ok"] == 3 and out["detected"] == [1]
+    assert out["launched_after_departure"] is False and out["local_gpu_ok_after"] and out["detect_s"] < 10

@@ -153,11 +153,13 @@ class SymmetricHeap:
             ok = ok and bool(flag.value)
         return ok
 
-    def close(self):
+    def close(self, collective: bool = True):
+        """Unmap the peers' slabs and free this rank's.  ``collective=False`` skips the barrier with the peers:
+        for a rank whose peers are known to be gone, or that has agreed on the order of frees by other means."""
         import torch
 
         if self._native is not None and self.base:
-            if self.world > 1 and self.cpu_group is not None:
+            if collective and self.world > 1 and self.cpu_group is not None:
                 import torch.distributed as dist
 
                 torch.cuda.synchronize()
