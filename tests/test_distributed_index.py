@@ -134,3 +134,52 @@ def test_owner_scorer_serves_independent_queries():
     out = mgr.dict()
     mp.spawn(_owner_main, args=(world, _free_port(), out), nprocs=world, join=True)
     assert dict(out) == {0: True, 1: True}
+
+
+def _collective_owner_main(rank, world, port, out):
+    import torch.distributed as dist
+    from ulacache_b200.flashag import create_index_transport
+    from ulacache_b200.indexer.nccl import CollectiveIndexOwner, local_score_columns
+
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    owner = create_index_transport("nccl", group=dist.group.WORLD, rank=rank, world=world, max_rows=6, cols=128,
+                                   device="cpu")
+    assert isinstance(owner, CollectiveIndexOwner) and owner.local_columns == local_score_columns(4, 2) == 128
+    ws = owner.gathered_workspace.data_ptr()
+    for q in (6, 3):                                         # a full and a partial prefix of the same workspace
+        local = torch.full((q, 128), float(rank + 1)) + torch.arange(q)[:, None]
+        got = owner.all_gather_scores(local)
+        assert got.shape == (world, q, 128) and got.data_ptr() == ws
+        for r in range(world):
+            assert torch.equal(got[r], torch.full((q, 128), float(r + 1)) + torch.arange(q)[:, None])
+    assert owner.calls == 2
+    owner.validate_bounds(6, 4)
+    errors = 0
+    for bad in (lambda: owner.validate_bounds(6, 8),
+                lambda: owner.all_gather_into_tensor(torch.zeros(7, 128)),               # beyond the bound
+                lambda: owner.all_gather_into_tensor(torch.zeros(6, 128).t()),           # not contiguous
+                lambda: owner.all_gather_into_tensor(torch.zeros(6, 128, dtype=torch.float64)),
+                lambda: owner.all_gather_into_tensor(torch.zeros(2, 128), output=torch.zeros(4, 128))):
+        try:
+            bad()
+        except ValueError:
+            errors += 1
+    with owner.graph_capture() as o:
+        assert o is owner
+    owner.close()
+    owner.close()                                            # idempotent
+    try:
+        owner.all_gather_scores(torch.zeros(2, 128))
+    except RuntimeError:
+        errors += 1
+    out[rank] = errors
+    dist.destroy_process_group()
+
+
+def test_collective_index_owner_gathers_into_its_own_workspace():
+    world = 2
+    mgr = mp.Manager()
+    out = mgr.dict()
+    mp.spawn(_collective_owner_main, args=(world, _free_port(), out), nprocs=world, join=True)
+    assert dict(out) == {0: 6, 1: 6}

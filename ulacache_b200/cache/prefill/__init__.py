@@ -8,4 +8,5 @@ from .buffers import PrefillWindow, PrefillWindowPair  # noqa: F401
 from .leases import WindowLeases  # noqa: F401
 from .plans import PrefillChunkPlan, plan_prefill_chunks  # noqa: F401
 from .reader import ReadOnlyPrefillReader  # noqa: F401
-from .window import SelectionWindowMap  # noqa: F401
+from .window import (PrefillReadPlan, PrefillRecordWindow, SelectionWindowMap, WindowedPrefillReader,  # noqa: F401
+                     compact_selection, shared_union)

@@ -250,11 +250,17 @@ class LineScoreAllGather(IndexTransport):
 
 
 def create_index_transport(kind: str, *, heap=None, group=None, rank: int = 0, world: int = 1, max_rows: int = 0,
-                           cols: int = 0, topk: int = 0):
+                           cols: int = 0, topk: int = 0, device=None, cpu_group=None):
     """``kind``: "candidates" (peer-stored top-k candidates, the default product path), "tagged"
     (barrier-free score all-gather in 128-byte lines), "tagged_words" (8-byte words) or "nccl"
-    (library all-gather)."""
+    (library all-gather; with ``device`` and the bounds ``max_rows`` x ``cols`` local columns it is the
+    workspace-owning form that a captured graph can replay)."""
     if kind == "nccl" or (kind in ("tagged", "tagged_words") and heap is None):
+        if kind == "nccl" and device is not None and max_rows > 0 and cols > 0 and cols % 64 == 0:
+            from ..indexer.nccl import CollectiveIndexOwner
+
+            return CollectiveIndexOwner(group, rank=rank, world=world, max_queries=max_rows,
+                                        max_page_width=cols // 64 * world, device=device, cpu_group=cpu_group)
         return CollectiveScoreAllGather(group, rank, world)
     if kind == "tagged":
         return LineScoreAllGather(heap, max_rows, cols)

@@ -95,6 +95,13 @@ class DistributedIndexScorer:
         """Logical token positions int32 [rows, topk] (-1 padded) of the global top-k."""
         p = self.plan
         if p.always_first or p.always_recent or p.transport != "candidates":
+            if self.transport is None and p.transport == "nccl" and p.ranks > 1 and self.group is not None:
+                # the library transport owns one workspace sized from the plan (no allocation per call)
+                from .nccl import CollectiveIndexOwner
+
+                self.transport = CollectiveIndexOwner(self.group, rank=self.rank, world=p.ranks, max_queries=p.rows,
+                                                      max_page_width=p.local_columns // p.page_tokens * p.ranks,
+                                                      device=local_scores.device)
             gathered = (self.transport.all_gather_scores(local_scores) if self.transport is not None
                         else _all_gather(local_scores, self.group, p.ranks))
             return self.layout.select(gathered, lengths, p.topk, always_first=p.always_first,
