@@ -104,8 +104,11 @@ class DistributedIndexScorer:
                                                       device=local_scores.device)
             gathered = (self.transport.all_gather_scores(local_scores) if self.transport is not None
                         else _all_gather(local_scores, self.group, p.ranks))
-            return self.layout.select(gathered, lengths, p.topk, always_first=p.always_first,
-                                      always_recent=p.always_recent)
+            from .topk import topk_rank_major
+
+            # (on GPUs: one radix-select launch over the rank-major scores with a shared index row)
+            return topk_rank_major(gathered, lengths, p.topk, self.own, always_first=p.always_first,
+                                   always_recent=p.always_recent)
         val, tok = _local_candidates(local_scores, self.local_lengths(lengths), p.topk, self.own, self.rank)
         if self.transport is not None and hasattr(self.transport, "exchange"):
             cv, ct = self.transport.exchange(tok, val)
