@@ -43,11 +43,16 @@ class BoundaryTransaction:
 
 
 class RequestPagePool:
-    def __init__(self, device_pages: int, host_pages: int, logical_pages: int):
+    def __init__(self, device_pages: int, host_pages: int, logical_pages: int, reserved_device_pages=()):
+        """``reserved_device_pages``: device pages that are never handed out (a sentinel page that padded
+        page-table entries may point at, pages another allocator owns)."""
         if device_pages < 1 or host_pages < 0 or logical_pages < 1:
             raise ValueError("page counts must be positive")
         self.device_pages, self.host_pages, self.logical_pages = device_pages, host_pages, logical_pages
-        self.free_device = list(range(device_pages - 1, -1, -1))
+        self.reserved_device_pages = tuple(sorted(set(int(p) for p in reserved_device_pages)))
+        if any(not 0 <= p < device_pages for p in self.reserved_device_pages):
+            raise ValueError("reserved device pages must lie inside the device pool")
+        self.free_device = [p for p in range(device_pages - 1, -1, -1) if p not in self.reserved_device_pages]
         self.free_host = list(range(host_pages - 1, -1, -1))
         self.free_logical = list(range(logical_pages - 1, -1, -1))
         self.where: Dict[int, Tuple[str, int]] = {}          # logical page -> ("d"|"h", physical page)
@@ -68,6 +73,10 @@ class RequestPagePool:
             if tier == "d":
                 m[lp] = phys
         return m
+
+    @property
+    def usable_device_pages(self) -> int:
+        return self.device_pages - len(self.reserved_device_pages)
 
     def resident_pages(self, request: int) -> int:
         return sum(1 for lp in self.pages_of.get(request, ()) if self.where[lp][0] == "d")

@@ -11,24 +11,29 @@ from __future__ import annotations
 
 
 class PageExchangeExecutor:
-    def __init__(self, storage, *, stream=None):
+    def __init__(self, storage, *, stream=None, extra_storages=()):
+        """``storage``: the record pages; ``extra_storages``: further page pools that move with the same
+        page numbers (the Index pages of the anchor layers).  Each has ``device_pool`` / ``host_pool``
+        ``[layers, pages, page_bytes]``."""
         self.storage = storage
+        self.storages = (storage,) + tuple(extra_storages)
         self.stream = stream
         self.bytes_d2h = 0
         self.bytes_h2d = 0
 
     def _run_wave(self, wave):
-        st = self.storage
-        per_page = st.page_bytes * st.layers
-        for _, dp, hp in wave.offloads:
-            st.host_pool[:, hp].copy_(st.device_pool[:, dp], non_blocking=True)
-            self.bytes_d2h += per_page
-        for _, hp, dp in wave.onloads:
-            st.device_pool[:, dp].copy_(st.host_pool[:, hp], non_blocking=True)
-            self.bytes_h2d += per_page
+        for st in self.storages:
+            per_page = st.page_bytes * st.layers
+            for _, dp, hp in wave.offloads:
+                st.host_pool[:, hp].copy_(st.device_pool[:, dp], non_blocking=True)
+                self.bytes_d2h += per_page
+            for _, hp, dp in wave.onloads:
+                st.device_pool[:, dp].copy_(st.host_pool[:, hp], non_blocking=True)
+                self.bytes_h2d += per_page
 
-    def execute(self, pool, txn, *, page_map_out=None):
-        """Run every wave of ``txn``, commit it, and refresh ``page_map_out`` (device int32) if given."""
+    def move(self, txn):
+        """Run every wave of ``txn`` (bytes only; nothing is committed or published).  On GPUs the copies run
+        on the boundary stream and the current stream waits for them."""
         import torch
 
         use_stream = self.stream is not None and self.storage.device_pool.is_cuda
@@ -41,7 +46,12 @@ class PageExchangeExecutor:
         else:
             for wave in txn.waves:
                 self._run_wave(wave)
+        return txn.moved_pages
+
+    def execute(self, pool, txn, *, page_map_out=None):
+        """Run every wave of ``txn``, commit it, and refresh ``page_map_out`` (device int32) if given."""
+        moved = self.move(txn)
         pool.commit(txn)
         if page_map_out is not None:
             page_map_out.copy_(pool.page_map(), non_blocking=True)
-        return txn.moved_pages
+        return moved
