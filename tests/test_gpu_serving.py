@@ -51,3 +51,46 @@ def test_snapshot_bank_restores_a_cache_that_decodes_the_same_tokens(native, tmp
 
     assert kv_bank.main(["--tiny", "--layers", "3", "--batch", "3", "--prompt-len", "700", "--steps", "8",
                          "--dir", str(tmp_path / "bank")]) == 0
+
+
+def test_recorded_trajectory_replays_through_the_decode_engine(native, monkeypatch):
+    """Record six natural greedy steps, then replay them into a fresh engine: the engine presents the same
+    requests at the same positions every step, decodes the recorded tokens, and produces the same samples."""
+    monkeypatch.setenv("ULC_DETERMINISTIC", "1")
+    from ulacache_b200.models.dsa_moe import DsaMoeConfig
+    from ulacache_b200.serving.engine import DecodeEngine
+    from ulacache_b200.tools.fixed_output import ReplayMismatch, ReplayTrace, TraceTokenReplay
+
+    cfg = DsaMoeConfig().tiny(layers=2)
+    B, prompt, steps = 3, 200, 6
+
+    def engine():
+        e = DecodeEngine(cfg, batch=B, prompt_len=prompt, max_new_tokens=steps + 2, use_graph=False)
+        e.fill_synthetic()
+        return e
+
+    eng = engine()
+    first = eng.batch.tokens.clone()
+    natural = []
+    for _ in range(steps):
+        out = eng.step_device()
+        natural.append(out.clone())
+        eng.batch.tokens.copy_(out)
+    eng.close()
+    keys = [f"r0.{i}" for i in range(B)]
+    outputs = {k: [int(natural[s][i]) for s in range(steps)] for i, k in enumerate(keys)}
+    trace = ReplayTrace.from_token_run(attention_dp=1, repeat=0, rank=0, keys=keys, input_tokens=[prompt] * B,
+                                       outputs=outputs)
+
+    eng2 = engine()
+    eng2.batch.tokens.copy_(first)
+    rp = TraceTokenReplay(trace, attention_dp=1, rank=0)
+    seen = []
+    orig = rp.sample
+    rp.sample = lambda nat: (seen.append(nat.clone()), orig(nat))[1]
+    receipt = eng2.run_replay(rp, "cohort", keys=keys)
+    assert receipt["complete"] and receipt["frames"] == steps and receipt["forward_calls"] == steps
+    assert all(torch.equal(a, b) for a, b in zip(seen, natural))       # same inputs, same model: same samples
+    with pytest.raises((ReplayMismatch, RuntimeError)):                 # the recording is used up
+        eng2.run_replay(rp, "cohort", keys=keys, steps=1)
+    eng2.close()

@@ -177,3 +177,64 @@ def test_publish_copies_to_both_tiers_cpu():
     assert torch.equal(dev_plane[:, int(loc[0])], staging[:, 3]) and torch.equal(dev_plane[:, int(loc[2])], staging[:, 1])
     assert torch.equal(host_plane[:, -int(loc[1]) - 2], staging[:, 0])
     assert int(dev_plane.sum()) == int(staging[:, 3].sum()) + int(staging[:, 1].sum())
+
+
+def test_recorded_cohort_replays_check_order_positions_and_hash(tmp_path):
+    import torch
+    from ulacache_b200.tools.fixed_output import (MTP_SCHEMA, ReplayMismatch, ReplayTrace, TraceMTPReplay,
+                                                  TraceTokenReplay, force_logits)
+
+    outputs = {"a": [5, 6, 7, 8], "b": [9, 10, 11, 12]}
+    trace = ReplayTrace.from_token_run(attention_dp=2, repeat=0, rank=1, keys=["a", "b"], input_tokens=[100, 40],
+                                       outputs=outputs)
+    sha = trace.save(str(tmp_path / "t.json.gz"))
+    again = ReplayTrace.load(str(tmp_path / "t.json.gz"))
+    assert again.sha256 == sha and not again.speculative
+    rp = TraceTokenReplay(again, attention_dp=2, rank=1)
+    for step in range(4):
+        rp.begin("c0", repeat=0, keys=["a", "b"], seq_lens=[100 + step, 40 + step], trace_sha256=sha)
+        got = rp.sample(torch.zeros(2, dtype=torch.int64))
+        assert got.tolist() == [outputs["a"][step], outputs["b"][step]]
+        with pytest.raises(ReplayMismatch):
+            rp.sample(torch.zeros(2, dtype=torch.int64))            # one sampler call per step
+        rp.end()
+    r = rp.receipt("c0")
+    assert r["complete"] and r["frames"] == r["expected_frames"] == 4 and not r["natural_accuracy_claimed"]
+    with pytest.raises(ReplayMismatch):                              # past the recorded budget
+        rp.begin("c0", repeat=0, keys=["a", "b"], seq_lens=[104, 44])
+    other = TraceTokenReplay(again, attention_dp=2, rank=1)
+    with pytest.raises(ReplayMismatch):                              # a different request order is a different workload
+        other.begin("c1", repeat=0, keys=["b", "a"], seq_lens=[40, 100])
+    with pytest.raises(ReplayMismatch):
+        other.begin("c1", repeat=0, keys=["a", "b"], seq_lens=[100, 40], trace_sha256="0" * 64)
+    with pytest.raises(ReplayMismatch):
+        again.episode(4, 0, 2, 1)
+    with pytest.raises(ValueError):
+        ReplayTrace(dict(schema="ulc-fixed-output-replay-v1", speculative=False, output_tokens=3, cases={},
+                         episodes={"e": dict(keys=["a"], input_tokens=[1], saved_bootstrap_tokens=0,
+                                             expected_output_ids={"a": [1, 2]})}))
+
+    frames = [dict(keys=["a", "b"], seq_lens=[10, 20], draft_tokens=[[1, 2, 3], [4, 5, 6]], accept_lens=[3, 1],
+                   emitted=[[1, 2, 3], [4]]),
+              dict(keys=["a"], seq_lens=[13], draft_tokens=[[7, 8, 9]], accept_lens=[2], emitted=[[7, 8]])]
+    mtp = ReplayTrace(dict(schema=MTP_SCHEMA, forced_acceptance=True, output_tokens=8, cases={"1:0:2:0": "e"},
+                           episodes={"e": dict(steps=2, verify_width=3, batch=2, frames=frames)}))
+    mr = TraceMTPReplay(mtp, attention_dp=1, rank=0)
+    d = mr.draft("c", repeat=0, keys=["a", "b"], seq_lens=[10, 20], steps=2)
+    assert d.tolist() == [[1, 2, 3], [4, 5, 6]]
+    with pytest.raises(ReplayMismatch):
+        mr.draft("c", repeat=0, keys=["a", "b"], seq_lens=[10, 20], steps=2)      # overlapping step
+    tok, ln = mr.sample(torch.zeros(2, 3, dtype=torch.int32), torch.zeros(2, dtype=torch.int32))
+    assert tok.tolist() == [[1, 2, 3], [4, -1, -1]] and ln.tolist() == [3, 1]
+    d = mr.draft("c", repeat=0, keys=["a"], seq_lens=[13], steps=2)
+    tok, ln = mr.sample(torch.zeros(1, 3, dtype=torch.int32), torch.zeros(1, dtype=torch.int32))
+    assert tok.tolist() == [[7, 8, -1]] and mr.completed("c") and mr.receipt("c")["forced_acceptance"]
+    with pytest.raises(ValueError):
+        ReplayTrace(dict(schema=MTP_SCHEMA, forced_acceptance=True, output_tokens=8, cases={},
+                         episodes={"e": dict(steps=2, verify_width=4, batch=1, frames=[])}))
+
+    logits = torch.randn(2, 16)
+    force_logits(logits, [[3, 4], [9]], [1, 0])
+    assert logits.argmax(1).tolist() == [4, 9] and int(torch.isinf(logits).sum()) == 30
+    with pytest.raises(ReplayMismatch):
+        force_logits(torch.randn(1, 4), [[7]], [0])

@@ -230,6 +230,25 @@ class DecodeEngine:
         torch.cuda.current_stream().synchronize()
         return self.host_out
 
+    def run_replay(self, replay, cohort, *, repeat: int = 0, keys=None, steps=None):
+        """Decode a RECORDED token trajectory (``tools.fixed_output.TraceTokenReplay``): every step runs the
+        full model and sampler, then the recorded tokens replace the samples as the next step's inputs, so
+        two cache methods (or two layouts) decode exactly the same workload.  The replay checks request
+        order and sequence positions at every step.  Returns the replay's receipt."""
+        import torch
+
+        keys = list(keys) if keys is not None else [f"r{self.rank}.{i}" for i in range(self.batch.tokens.numel())]
+        n = steps if steps is not None else replay.trace.data["output_tokens"]
+        for _ in range(n):
+            lens = self.batch.lengths[: len(keys)].tolist()
+            replay.begin(cohort, repeat=repeat, keys=keys, seq_lens=lens, trace_sha256=replay.trace.sha256)
+            natural = self.step_device()
+            forced = replay.sample(natural)
+            self.batch.tokens.copy_(forced.to(self.batch.tokens.dtype), non_blocking=True)
+            replay.end()
+        torch.cuda.current_stream().synchronize()
+        return replay.receipt(cohort)
+
     def check(self):
         from ..ops import _native as N
 
