@@ -234,7 +234,7 @@ class NativePagedResidency(CacheEngine):
         """{storage address: bytes} of every device allocation the cache holds (payload and metadata);
         aliases of one storage count once."""
         inv = {}
-        tensors = [st.gpu for st in self.storages] + [t for t in self._metadata_tensors() if t.device == self.device]
+        tensors = [st.gpu for st in self.storages] + self._metadata_tensors()
         for t in tensors:
             if t is not None and t.numel() and t.device.type == self.device.type:
                 s = t.untyped_storage()
