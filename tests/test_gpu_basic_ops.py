@@ -47,7 +47,7 @@ def test_batched_gemm_with_quantising_epilogue(native, T, heads):
     assert ((got - want).abs() > 1e-3 * want.abs().max()).float().mean().item() < 0.02
 
 
-@pytest.mark.parametrize("mode", ["row", "cluster"])
+@pytest.mark.parametrize("mode", ["row", "cluster", "rows"])
 @pytest.mark.parametrize("rows,Lmax,k", [(3, 100, 128), (4, 5000, 256), (2, 131072, 2048), (5, 40000, 2048),
                                          (32, 32768, 2048)])
 def test_topk_matches_reference(native, rows, Lmax, k, mode):
@@ -65,7 +65,7 @@ def test_topk_matches_reference(native, rows, Lmax, k, mode):
         assert sorted(out[r].tolist()) == sorted(ref[r].tolist())
 
 
-@pytest.mark.parametrize("mode", ["row", "cluster"])
+@pytest.mark.parametrize("mode", ["row", "cluster", "rows"])
 def test_topk_narrow_score_range(native, mode):
     """Scores packed into one or two coarse bins (what ReLU-weighted index scores look like): the
     threshold bin then holds more elements than the shared-memory candidate store."""
@@ -83,7 +83,7 @@ def test_topk_narrow_score_range(native, mode):
         assert sorted(out[r].tolist()) == sorted(ref[r].tolist())
 
 
-@pytest.mark.parametrize("mode", ["row", "cluster"])
+@pytest.mark.parametrize("mode", ["row", "cluster", "rows"])
 def test_topk_ties_and_transform(native, mode):
     s = torch.zeros(2, 9000, device="cuda")
     s[0, 100:200] = 1.0
@@ -120,6 +120,53 @@ def test_topk_histogram_method_matches_reference(native, rows, Lmax, k):
             picked = out[r][out[r] >= 0].long()
             assert torch.equal(vals[r][out[r] >= 0], s[r][picked])
         assert topk.workspace_is_clean(topk.workspace(rows, "cuda"), rows)
+
+
+def test_topk_many_rows_kernel(native):
+    """The throughput kernel on what prefill and large batches give it: hundreds of rows (more rows than
+    CTAs), ragged lengths around every internal boundary (k, the candidate store, chunk ends), rows whose
+    stride breaks 16-byte alignment, heavy ties, -inf runs, values, candidate lists and the paged transform."""
+    torch.manual_seed(11)
+    rows, L, k = 330, 20011, 2048
+    s = torch.randn(rows, L, device="cuda")
+    s[5] = 0.25                                            # every element tied
+    s[6, ::3] = 7.0                                        # a third of the row tied at the top
+    s[7, 4000:] = float("-inf")
+    s[8] = torch.rand(L, device="cuda").round(decimals=2)  # 101 distinct values
+    lengths = torch.randint(1, L + 1, (rows,), device="cuda", dtype=torch.int32)
+    for r, n in enumerate([0, 1, 2047, 2048, 2049, 8191, 8192, 8193, 16384, 16385, L]):
+        lengths[10 + r] = n
+    lengths[5:9] = L
+    vals = torch.empty(rows, k, device="cuda")
+    counts = torch.empty(rows, dtype=torch.int32, device="cuda")
+    out = topk.topk(s, k, lengths, out_val=vals, out_count=counts)      # auto: this many rows take the throughput kernel
+    torch.cuda.synchronize()
+    ref = topk.topk_reference(s, k, lengths)
+    for r in range(rows):
+        assert sorted(out[r].tolist()) == sorted(ref[r].tolist()), r
+        keep = out[r] >= 0
+        assert torch.equal(vals[r][keep], s[r][out[r][keep].long()])
+    assert torch.equal(counts.cpu(), lengths.clamp(max=k).cpu())
+    topk.set_launch_mode("rows")
+    try:
+        # candidate-list mode with an index transform, few rows, explicit mode
+        cv = torch.randn(3, 9000, device="cuda")
+        ci = torch.randint(0, 50000, (3, 9000), device="cuda", dtype=torch.int32)
+        got = topk.topk(cv, 512, in_idx=ci)
+        want = topk.topk_reference(cv, 512, in_idx=ci)
+        assert all(sorted(got[r].tolist()) == sorted(want[r].tolist()) for r in range(3))
+        # long rows: several chunks, filter from samples
+        big = torch.randn(4, 150001, device="cuda")
+        got = topk.topk(big, 2048)
+        want = topk.topk_reference(big, 2048)
+        assert all(sorted(got[r].tolist()) == sorted(want[r].tolist()) for r in range(4))
+        # a narrow range: the sample's filter bin holds most of the row (falls back to the exact pass over the row)
+        narrow = 1.0 + 0.01 * torch.rand(3, 40000, device="cuda")
+        got = topk.topk(narrow, 2048)
+        want = topk.topk_reference(narrow, 2048)
+        assert all(sorted(got[r].tolist()) == sorted(want[r].tolist()) for r in range(3))
+    finally:
+        topk.set_launch_mode("auto")
 
 
 def _single_rank_view(pool, directory, rec_bytes):

@@ -799,9 +799,267 @@ static int launch_topk(const TopkArgs& a, int rows, int cap, cudaStream_t stream
   return static_cast<int>(e != cudaSuccess ? e : cudaGetLastError());
 }
 
+// ------------------------------------------------------------------------------------------------
+// Throughput form for MANY rows (prefill chunks, large batches): one CTA per row, no cluster, no
+// communication between CTAs, CTAs walk the rows in a grid-stride loop.
+//
+//  1. 2048 evenly spaced samples of the row go into the 2048-bin windowed histogram; the bin that
+//     holds the sample of rank 1.75 k / n * 2048 becomes the filter bin.
+//  2. The row is streamed once (16 elements per thread and chunk, float4 loads); elements at or
+//     above the filter bin (about 1.75 k of them) are compacted into shared memory with a block scan
+//     (no atomics).  Rows of up to 8192 elements skip the filter and keep everything.
+//  3. The exact k-th element of the survivors is found by radix levels over the 64-bit composite
+//     (key, ~position): 11 + 11 + 10 key bits, then, only when equal keys straddle the cut,
+//     11 + 11 + 10 position bits.  A level stops the search as soon as its threshold bin holds exactly
+//     the number of elements still wanted.  Ties therefore go to the lowest position.
+//  4. Survivors at or above the threshold composite are written out through a block scan.
+//  If a sample misjudged the row (fewer than k survivors) or equal values flood the candidate store,
+//  steps 3 and 4 run over the row in global memory instead (same code, another element source).
+constexpr int kRowsThreads = 512;
+constexpr int kRowsWarps = kRowsThreads / 32;
+constexpr int kRowsCand = 8192;
+constexpr int kRowsSamples = 2048;
+constexpr int kRowsPerThread = 16;
+constexpr int kRowsChunk = kRowsThreads * kRowsPerThread;
+
+struct RowsShared {
+  uint32_t cand_key[kRowsCand];
+  int32_t cand_pos[kRowsCand];
+  uint32_t hist[kTopkBins];
+  uint32_t warp_sums[kRowsWarps];
+  uint32_t total;
+  uint32_t sel_bin, sel_above, sel_count;
+};
+constexpr int kRowsSmem = static_cast<int>(sizeof(RowsShared));
+
+// exclusive scan of one value per thread over the CTA; *total (shared) receives the sum
+__device__ __forceinline__ uint32_t rows_block_scan(uint32_t v, RowsShared& s) {
+  const uint32_t lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const uint32_t incl = warp_inclusive_scan(v);
+  __syncthreads();                                   // the previous scan's warp_sums / total are done with
+  if (lane == 31) s.warp_sums[warp] = incl;
+  __syncthreads();
+  if (warp == 0) {
+    const uint32_t w = lane < kRowsWarps ? s.warp_sums[lane] : 0u;
+    const uint32_t wi = warp_inclusive_scan(w);
+    if (lane < kRowsWarps) s.warp_sums[lane] = wi - w;
+    if (lane == kRowsWarps - 1) s.total = wi;
+  }
+  __syncthreads();
+  return s.warp_sums[warp] + incl - v;
+}
+
+// Among the bins [0, nb) of s.hist, counted from the TOP: the bin b with
+// (elements in bins above b) < need <= (elements in bins >= b).  Results in s.sel_*; s.sel_count = 0 and
+// s.sel_bin = nb when the histogram holds fewer than `need` elements.  Every thread calls it.
+__device__ __forceinline__ void rows_find_bin(RowsShared& s, int nb, uint32_t need) {
+  const int per = nb / kRowsThreads;                 // 4 (2048 bins) or 2 (1024 bins)
+  const int t = threadIdx.x;
+  uint32_t h[4];
+  uint32_t sum = 0;
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    h[j] = j < per ? s.hist[nb - 1 - (t * per + j)] : 0u;     // reversed: j-th bin from the top of my range
+    sum += h[j];
+  }
+  if (t == 0) { s.sel_bin = static_cast<uint32_t>(nb); s.sel_above = 0; s.sel_count = 0; }
+  uint32_t run = rows_block_scan(sum, s);            // (its barriers also order the reset above)
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    if (j < per) {
+      if (run < need && need <= run + h[j]) {
+        s.sel_bin = static_cast<uint32_t>(nb - 1 - (t * per + j));
+        s.sel_above = run;
+        s.sel_count = h[j];
+      }
+      run += h[j];
+    }
+  }
+  __syncthreads();
+}
+
+// Histogram add of the lanes with `pred`.  Plain shared-memory atomics: aggregating equal bins of a warp first
+// (`match.any` + one atomic per distinct bin) measured SLOWER here (10.8 k against 7.3 k cycles for the three
+// levels of a 32K row), the match instruction costing more than the conflicts it removes.
+__device__ __forceinline__ void rows_hist_add(uint32_t* hist, uint32_t bin, bool pred) {
+  if (pred) atomicAdd(&hist[bin], 1u);
+}
+
+struct RowsCandSource {
+  const RowsShared* s;
+  uint32_t n;
+  __device__ __forceinline__ uint64_t at(uint32_t i) const {
+    return (static_cast<uint64_t>(s->cand_key[i]) << 32) | static_cast<uint32_t>(~s->cand_pos[i]);
+  }
+};
+struct RowsGlobalSource {
+  const float* x;
+  uint32_t n;
+  __device__ __forceinline__ uint64_t at(uint32_t i) const {
+    return (static_cast<uint64_t>(order_key(x[i])) << 32) | static_cast<uint32_t>(~i);
+  }
+};
+
+// Steps 3 and 4 over `src`; exactly k elements are written (src.n > k).
+template <class Source>
+__device__ __forceinline__ void rows_select_emit(RowsShared& s, const Source& src, int k, int32_t* oi, float* ov,
+                                                 const TopkXform& xf) {
+  const int t = threadIdx.x;
+  uint64_t prefix = 0, mask = 0;
+  uint32_t need = static_cast<uint32_t>(k);
+  for (int level = 0; level < 6; ++level) {
+    const int shift = level == 0 ? 53 : level == 1 ? 42 : level == 2 ? 32 : level == 3 ? 21 : level == 4 ? 10 : 0;
+    const int nb = (level == 2 || level == 5) ? 1024 : 2048;
+    for (int i = t; i < nb; i += kRowsThreads) s.hist[i] = 0;
+    __syncthreads();
+    for (uint32_t i0 = 0; i0 < src.n; i0 += kRowsThreads) {
+      const uint32_t i = i0 + static_cast<uint32_t>(t);
+      const uint64_t c = i < src.n ? src.at(i) : 0ull;
+      rows_hist_add(s.hist, static_cast<uint32_t>(c >> shift) & static_cast<uint32_t>(nb - 1), i < src.n && (c & mask) == prefix);
+    }
+    __syncthreads();
+    rows_find_bin(s, nb, need);
+    const uint32_t bin = s.sel_bin, above = s.sel_above, in_bin = s.sel_count;
+    __syncthreads();                                 // everyone has read the result before the next level resets it
+    need -= above;
+    prefix |= static_cast<uint64_t>(bin) << shift;
+    mask |= static_cast<uint64_t>(nb - 1) << shift;
+    if (in_bin == need) break;                       // everything that matches the prefix is selected
+  }
+  TOPK_T(4);
+  // selected: masked composite >= prefix.  Per-thread counts, one scan, ordered writes.
+  uint32_t base = 0;
+  for (uint32_t i0 = 0; i0 < src.n; i0 += kRowsChunk) {
+    uint32_t cnt = 0;
+    uint32_t flags = 0;
+#pragma unroll
+    for (int j = 0; j < kRowsPerThread; ++j) {
+      const uint32_t i = i0 + static_cast<uint32_t>(j * kRowsThreads + t);
+      if (i < src.n && (src.at(i) & mask) >= prefix) { flags |= 1u << j; ++cnt; }
+    }
+    uint32_t at = base + rows_block_scan(cnt, s);
+    base += s.total;
+#pragma unroll
+    for (int j = 0; j < kRowsPerThread; ++j) {
+      if (flags & (1u << j)) {
+        const uint64_t c = src.at(i0 + static_cast<uint32_t>(j * kRowsThreads + t));
+        write_out(oi, ov, k, at++, static_cast<int32_t>(~static_cast<uint32_t>(c)), static_cast<uint32_t>(c >> 32), xf);
+      }
+    }
+  }
+}
+
+__global__ void __launch_bounds__(kRowsThreads, 2)
+topk_rows_kernel(const TopkArgs a, const int rows) {
+  extern __shared__ __align__(16) uint8_t rows_smem_raw[];
+  RowsShared& s = *reinterpret_cast<RowsShared*>(rows_smem_raw);
+  const int t = threadIdx.x;
+  const int k = a.k;
+  for (int row = blockIdx.x; row < rows; row += gridDim.x) {
+    const float* x = a.scores + static_cast<size_t>(row) * a.row_stride;
+    TopkXform xf;
+    xf.in_idx = a.in_idx ? a.in_idx + static_cast<size_t>(row) * a.in_idx_stride : nullptr;
+    xf.table = a.xform ? a.xform + static_cast<size_t>(row) * a.xform_stride : nullptr;
+    xf.pages = a.pages ? a.pages + static_cast<size_t>(row / a.rows_per_request) * a.pages_stride : nullptr;
+    xf.ranks = a.ranks; xf.rank = a.rank; xf.drop_neg_inf = a.drop_neg_inf;
+    int32_t* oi = a.out_idx + static_cast<size_t>(row) * k;
+    float* ov = a.out_val ? a.out_val + static_cast<size_t>(row) * k : nullptr;
+    const int n = a.lengths ? min(max(a.lengths[row], 0), a.max_len) : a.max_len;
+    TOPK_T(0);
+    if (t == 0 && a.out_count) a.out_count[row] = min(n, k);
+    if (n <= k) {
+      for (int i = t; i < k; i += kRowsThreads) {
+        oi[i] = i < n ? xform_value(xf, i, x[i]) : -1;
+        if (ov) ov[i] = i < n ? x[i] : -INFINITY;
+      }
+      continue;
+    }
+    // ---- 1. filter bin from samples (rows that fit the candidate store keep everything) ----
+    uint32_t filter_bin = 0;
+    if (n > kRowsCand) {
+      for (int i = t; i < kTopkBins; i += kRowsThreads) s.hist[i] = 0;
+      __syncthreads();
+      for (int i = t; i < kRowsSamples; i += kRowsThreads) {           // (kRowsSamples is a multiple of the CTA size)
+        const int pos = static_cast<int>((static_cast<long long>(i) * n) / kRowsSamples);
+        rows_hist_add(s.hist, window_bin(order_key(x[pos])), true);
+      }
+      __syncthreads();
+      TOPK_T(1);
+      long long want = (7ll * k * kRowsSamples + 4ll * n - 1) / (4ll * n);          // ceil(1.75 k / n * samples)
+      want = want < 8 ? 8 : (want > kRowsSamples / 2 ? kRowsSamples / 2 : want);
+      rows_find_bin(s, kTopkBins, static_cast<uint32_t>(want));
+      filter_bin = s.sel_bin < static_cast<uint32_t>(kTopkBins) ? s.sel_bin : 0u;
+      __syncthreads();
+    }
+    TOPK_T(2);
+    // ---- 2. stream the row, compact the survivors ----
+    const bool vec = (reinterpret_cast<uintptr_t>(x) & 15) == 0;
+    uint32_t base = 0;
+    bool overflow = false;
+    for (int c0 = 0; c0 < n; c0 += kRowsChunk) {
+      float v[kRowsPerThread];
+#pragma unroll
+      for (int j = 0; j < kRowsPerThread / 4; ++j) {
+        const int i = c0 + (j * kRowsThreads + t) * 4;
+        if (vec && i + 3 < n) {
+          const float4 q = *reinterpret_cast<const float4*>(x + i);
+          v[4 * j] = q.x; v[4 * j + 1] = q.y; v[4 * j + 2] = q.z; v[4 * j + 3] = q.w;
+        } else {
+#pragma unroll
+          for (int e = 0; e < 4; ++e) v[4 * j + e] = i + e < n ? x[i + e] : 0.f;
+        }
+      }
+      uint32_t flags = 0, cnt = 0;
+#pragma unroll
+      for (int j = 0; j < kRowsPerThread; ++j) {
+        const int i = c0 + ((j >> 2) * kRowsThreads + t) * 4 + (j & 3);
+        if (i < n && window_bin(order_key(v[j])) >= filter_bin) { flags |= 1u << j; ++cnt; }
+      }
+      uint32_t at = base + rows_block_scan(cnt, s);
+      base += s.total;
+#pragma unroll
+      for (int j = 0; j < kRowsPerThread; ++j) {
+        if (flags & (1u << j)) {
+          if (at < static_cast<uint32_t>(kRowsCand)) {
+            s.cand_key[at] = order_key(v[j]);
+            s.cand_pos[at] = c0 + ((j >> 2) * kRowsThreads + t) * 4 + (j & 3);
+          }
+          ++at;
+        }
+      }
+      if (base > static_cast<uint32_t>(kRowsCand)) { overflow = true; break; }      // (uniform: base is the same in every thread)
+    }
+    __syncthreads();
+    TOPK_T(3);
+    // ---- 3 + 4. exact selection and output ----
+    if (!overflow && base >= static_cast<uint32_t>(k)) {
+      RowsCandSource src{&s, base};
+      rows_select_emit(s, src, k, oi, ov, xf);
+    } else {
+      RowsGlobalSource src{x, static_cast<uint32_t>(n)};
+      rows_select_emit(s, src, k, oi, ov, xf);
+    }
+    __syncthreads();                                 // the candidate store is free for the next row
+    TOPK_T(5);
+  }
+}
+
+static int launch_topk_rows(const TopkArgs& a, int rows, cudaStream_t stream) {
+  static PerDeviceOnce once;
+  int rc = ensure_dynamic_smem(reinterpret_cast<const void*>(topk_rows_kernel), kRowsSmem, once);
+  if (rc != 0) return rc;
+  int sms = 148, dev = 0;
+  cudaGetDevice(&dev);
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  const int grid = rows < 2 * sms ? rows : 2 * sms;
+  topk_rows_kernel<<<grid, kRowsThreads, kRowsSmem, stream>>>(a, rows);
+  return static_cast<int>(cudaGetLastError());
+}
+
 }  // namespace ulc
 
 static int g_topk_mode = 0;
+constexpr int kTopkManyRows = 48;   // rows from which the throughput kernel is taken
 
 extern "C" {
 
@@ -837,12 +1095,15 @@ int ulc_topk_ex(const float* scores, long long row_stride, const int32_t* length
   // each), then more while the launch still fits the machine in one wave.
   // mode: 0 = choose, 1 = one CTA per row, 2 = a cluster of eight per row.
   const int mode = g_topk_mode;
+  // many rows: the one-CTA-per-row throughput kernel (mode 3 forces it, any other explicit mode keeps it off)
+  if (mode == 3 || (mode == 0 && rows >= kTopkManyRows && max_len > 2 * k)) return launch_topk_rows(a, rows, stream);
   int cs = 1;
   while (cs < kTopkMaxCluster && static_cast<long long>(cs) * kTopkThreads * 16 < max_len) cs *= 2;
   while (cs < kTopkMaxCluster && static_cast<long long>(rows) * cs * 2 <= 2 * 148) cs *= 2;
   if (max_len <= 2 * k) cs = 1;       // short candidate lists: one CTA, nothing to share
   if (mode == 1) cs = 1;
   if (mode == 2) cs = kTopkMaxCluster;
+  if (mode == 12 || mode == 14) cs = mode - 10;     // (measurements: a forced cluster of two / four)
   // blocks of keys a CTA holds in shared memory: its whole share of the row when that is at most 32
   long long cap = (static_cast<long long>(max_len) + cs * kTopkThreads - 1) / (cs * kTopkThreads);
   cap = cap < 1 ? 1 : (cap > 32 ? 32 : cap);
@@ -897,7 +1158,8 @@ int ulc_topk_trace_read(long long* host) {
 }
 #endif
 
-// Launch shape override for tests and measurements: 0 = choose by size, 1 = one CTA per row, 2 = a cluster of eight per row.
+// Launch shape override for tests and measurements: 0 = choose by size, 1 = one CTA per row, 2 = a cluster of eight per row,
+// 3 = the many-rows throughput kernel.
 void ulc_topk_set_mode(int mode) { g_topk_mode = mode; }
 
 int ulc_topk(const float* scores, long long row_stride, const int32_t* lengths, int rows, int max_len,
