@@ -47,7 +47,7 @@ def test_batched_gemm_with_quantising_epilogue(native, T, heads):
     assert ((got - want).abs() > 1e-3 * want.abs().max()).float().mean().item() < 0.02
 
 
-@pytest.mark.parametrize("mode", ["row", "cluster", "rows"])
+@pytest.mark.parametrize("mode", ["row", "cluster", "rows", "rows_staged"])
 @pytest.mark.parametrize("rows,Lmax,k", [(3, 100, 128), (4, 5000, 256), (2, 131072, 2048), (5, 40000, 2048),
                                          (32, 32768, 2048)])
 def test_topk_matches_reference(native, rows, Lmax, k, mode):
@@ -65,7 +65,7 @@ def test_topk_matches_reference(native, rows, Lmax, k, mode):
         assert sorted(out[r].tolist()) == sorted(ref[r].tolist())
 
 
-@pytest.mark.parametrize("mode", ["row", "cluster", "rows"])
+@pytest.mark.parametrize("mode", ["row", "cluster", "rows", "rows_staged"])
 def test_topk_narrow_score_range(native, mode):
     """Scores packed into one or two coarse bins (what ReLU-weighted index scores look like): the
     threshold bin then holds more elements than the shared-memory candidate store."""
@@ -83,7 +83,7 @@ def test_topk_narrow_score_range(native, mode):
         assert sorted(out[r].tolist()) == sorted(ref[r].tolist())
 
 
-@pytest.mark.parametrize("mode", ["row", "cluster", "rows"])
+@pytest.mark.parametrize("mode", ["row", "cluster", "rows", "rows_staged"])
 def test_topk_ties_and_transform(native, mode):
     s = torch.zeros(2, 9000, device="cuda")
     s[0, 100:200] = 1.0
@@ -147,6 +147,17 @@ def test_topk_many_rows_kernel(native):
         keep = out[r] >= 0
         assert torch.equal(vals[r][keep], s[r][out[r][keep].long()])
     assert torch.equal(counts.cpu(), lengths.clamp(max=k).cpu())
+    for mode in ("rows", "rows_staged"):
+        topk.set_launch_mode(mode)
+        try:
+            got = topk.topk(s, k, lengths)                          # the same rows through each form explicitly
+            aligned = topk.topk(s[:, :20000].contiguous(), k)      # every row 16-byte aligned: all rows staged
+            torch.cuda.synchronize()
+        finally:
+            topk.set_launch_mode("auto")
+        assert all(sorted(got[r].tolist()) == sorted(ref[r].tolist()) for r in range(rows)), mode
+        ref_a = topk.topk_reference(s[:40, :20000], k)
+        assert all(sorted(aligned[r].tolist()) == sorted(ref_a[r].tolist()) for r in range(40)), mode
     topk.set_launch_mode("rows")
     try:
         # candidate-list mode with an index transform, few rows, explicit mode

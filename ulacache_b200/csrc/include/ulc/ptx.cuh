@@ -233,6 +233,12 @@ __device__ __forceinline__ void cp_async16_zfill(void* smem_dst, const void* gsr
                "l"(gsrc), "r"(n)
                : "memory");
 }
+// 16-byte copy of which only the first `src_bytes` (0 .. 16) are read; the rest of the destination is zero.
+__device__ __forceinline__ void cp_async16_partial(void* smem_dst, const void* gsrc, int src_bytes) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(smem_u32(smem_dst)),
+               "l"(gsrc), "r"(src_bytes)
+               : "memory");
+}
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
 template <int N>
 __device__ __forceinline__ void cp_async_wait() {

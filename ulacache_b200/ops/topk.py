@@ -133,6 +133,7 @@ def topk_paged_ids(scores, k, pages, *, rows_per_request=1, ranks=1, rank=0, out
 
 def set_launch_mode(mode="auto"):
     """Pin the launch shape of the CUDA top-k: ``"auto"`` (choose by rows and row length),
-    ``"row"`` (one CTA per row), ``"cluster"`` (a cluster of eight CTAs per row) or ``"rows"`` (the many-rows
-    throughput kernel: one CTA per row, sampled filter bin, block-scan compaction)."""
-    N.cuda().ulc_topk_set_mode(C.c_int({"auto": 0, "row": 1, "cluster": 2, "rows": 3}[mode]))
+    ``"row"`` (one CTA per row), ``"cluster"`` (a cluster of eight CTAs per row) or ``"rows"`` / ``"rows_staged"`` (the
+    many-rows throughput kernel: one CTA per row, sampled filter bin, block-scan compaction; streaming the row
+    from global memory, or staging it whole in shared memory with asynchronous copies)."""
+    N.cuda().ulc_topk_set_mode(C.c_int({"auto": 0, "row": 1, "cluster": 2, "rows": 3, "rows_staged": 4}[mode]))
