@@ -3,7 +3,7 @@
 fused residual-add + RMSNorm + fp8 quantiser, the attention split merge, the SwiGLU
 quantiser with and without the routed-row limit, and the batched per-head bf16 GEMMs.
 
-    python -m ulacache_b200.benchmarks.decode_small_kernels
+    python -m ulacache_b200.benchmarks.decode_small_kernels [--topk-forms]
 
 Each call is timed alone with CUDA events after a write of a 256 MB buffer (larger than
 L2), so the inputs come from HBM as they do inside a step that streams expert weights
@@ -34,11 +34,42 @@ def _time_flushed(fn, flush, *, warmup=5, iters=30):
     return ts[len(ts) // 2]
 
 
+def topk_forms():
+    """Every launch form of the stand-alone top-k over rows x context (k = 2048, normal scores): the cluster
+    kernel, the histogram pair, and the one-CTA-per-row kernels (streaming and staged).  CUDA events around 8
+    calls with a 256 MB write before each (its own time subtracted), one JSON line per shape."""
+    import torch
+    from ..ops import topk
+    from .common import time_cuda
+
+    torch.manual_seed(0)
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
+    for ctx in (32768, 65536, 131072):
+        for rows in (8, 32, 64, 128, 256, 1024, 2048):
+            if rows * ctx * 4 > (1 << 30):
+                continue
+            x = torch.randn(rows, ctx, device="cuda")
+            out = torch.empty(rows, 2048, dtype=torch.int32, device="cuda")
+            base = time_cuda(lambda: flush.zero_(), iters=8)
+            res = {}
+            for name in ("auto", "cluster", "rows", "rows_staged"):
+                topk.set_launch_mode(name)
+                try:
+                    res[name] = round(time_cuda(lambda: (flush.zero_(), topk.topk(x, 2048, out=out)), iters=8) - base, 1)
+                finally:
+                    topk.set_launch_mode("auto")
+            res["hist"] = round(time_cuda(lambda: (flush.zero_(), topk.topk(x, 2048, out=out, method="hist")), iters=8) - base, 1)
+            emit(kernel="topk_forms", rows=rows, length=ctx, k=2048, us=res)
+
+
 def main():
+    import sys
     import torch
     from ..ops import fp8, gemm, glue, topk
     from ..ops import prefill as P
 
+    if "--topk-forms" in sys.argv:
+        return topk_forms()
     dev = "cuda"
     torch.manual_seed(0)
     flush = torch.empty(64 << 20, dtype=torch.float32, device=dev)
