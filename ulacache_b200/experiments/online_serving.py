@@ -95,6 +95,11 @@ def build_trace(*, sessions, turns_lo, turns_hi, system_prefix, median_input, si
     return reqs
 
 
+import os as _os
+
+_os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")      # stdout carries the result line only
+
+
 def main():
     import torch
     from ..models.dsa_moe import DsaMoeConfig
