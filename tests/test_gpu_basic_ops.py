@@ -47,6 +47,39 @@ def test_batched_gemm_with_quantising_epilogue(native, T, heads):
     assert ((got - want).abs() > 1e-3 * want.abs().max()).float().mean().item() < 0.02
 
 
+def test_per_head_products_at_prefill_row_counts(native, monkeypatch):
+    """From 512 rows the per-head products take the library's batched GEMM; same results as the decode kernel
+    (bf16 rounding of fp32 sums), head-interleaved inputs and both output layouts."""
+    from ulacache_b200.ops import fp8
+
+    torch.manual_seed(2)
+    T, heads = 640, 8
+    qb = torch.randn(T, heads * 192, device="cuda", dtype=torch.bfloat16)
+    x = torch.as_strided(qb, (T, heads, 128), (qb.stride(0), 192, 1))             # the q_nope view of a fused projection
+    w = (torch.randn(heads, 512, 128, device="cuda") * 0.05).to(torch.bfloat16)
+    ref = torch.einsum("tbk,bnk->tbn", x.float(), w.float())
+    out_a = torch.empty(T, heads, 512, device="cuda", dtype=torch.bfloat16)        # token-major: copied out of the product
+    out_b = torch.empty(heads, T, 512, device="cuda", dtype=torch.bfloat16).transpose(0, 1)   # head-major storage: in place
+    assert gemm.many_rows(T)
+    gemm.batched_linear(x, w, out_a)
+    gemm.batched_linear(x, w, out_b)
+    monkeypatch.setenv("ULC_PREFILL_GEMM", "0")
+    out_k = gemm.batched_linear(x, w, torch.empty(T, heads, 512, device="cuda", dtype=torch.bfloat16))
+    monkeypatch.delenv("ULC_PREFILL_GEMM")
+    torch.cuda.synchronize()
+    tol = 0.02 * ref.abs().max().item()
+    for got in (out_a, out_b, out_k):
+        assert (got.float() - ref).abs().max().item() <= tol
+    o_lat = torch.randn(T, heads, 512, device="cuda", dtype=torch.bfloat16)
+    wv = (torch.randn(heads, 128, 512, device="cuda") * 0.05).to(torch.bfloat16)
+    q, sc = gemm.batched_linear_quant(o_lat, wv)
+    want_q, want_s = fp8.act_quant_reference(torch.einsum("tbk,bnk->tbn", o_lat.float(), wv.float()).reshape(T, heads * 128))
+    assert torch.allclose(sc, want_s, rtol=2e-2, atol=1e-6)
+    got = q.view(torch.float8_e4m3fn).float().view(T, heads, 128) * sc.view(T, heads, 1)
+    want = want_q.view(torch.float8_e4m3fn).float().view(T, heads, 128) * want_s.view(T, heads, 1)
+    assert (got - want).abs().max().item() <= 0.13 * want.abs().max().item()
+
+
 @pytest.mark.parametrize("mode", ["row", "cluster", "rows", "rows_staged"])
 @pytest.mark.parametrize("rows,Lmax,k", [(3, 100, 128), (4, 5000, 256), (2, 131072, 2048), (5, 40000, 2048),
                                          (32, 32768, 2048)])

@@ -57,7 +57,7 @@ def test_native_includes_resolve_in_tree():
     system = ("cuda", "cooperative_groups", "stdint.h", "stddef.h", "string.h", "stdio.h", "math.h", "mma.h", "stdlib.h",
               "assert.h", "limits.h", "float.h")
     std = {"algorithm", "cstdint", "cstring", "list", "map", "mutex", "string", "unordered_map", "vector", "atomic",
-           "cstdio", "cstdlib", "cmath", "utility", "type_traits"}
+           "cstdio", "cstdlib", "cmath", "utility", "type_traits", "chrono", "memory", "random", "thread"}
     checked = 0
     for root, _, files in os.walk(os.path.join(PKG, "csrc")):
         for f in files:

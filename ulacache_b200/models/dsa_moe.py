@@ -591,7 +591,10 @@ class DsaMoeModel:
         self._mark("attn.absorb gemm")
         # q_lat[b, h, :] = q_nope[b, h, :] @ W_UK[h], read in place from the projection output
         q_nope = torch.as_strided(qb, (B, heads, c.nope_dim), (qb.stride(0), c.nope_dim + c.rope_dim, 1))
-        q_lat = torch.empty((B, heads, c.kv_lora), dtype=torch.bfloat16, device=qb.device)
+        if gemm.many_rows(B):     # prefill-sized: head-major storage, which the library's batched product writes in place
+            q_lat = torch.empty((heads, B, c.kv_lora), dtype=torch.bfloat16, device=qb.device).transpose(0, 1)
+        else:
+            q_lat = torch.empty((B, heads, c.kv_lora), dtype=torch.bfloat16, device=qb.device)
         gemm.batched_linear(q_nope, w.w_uk_t, q_lat)
 
         # ---- indexer: store this token's key, score the context, take the top-k

@@ -42,6 +42,16 @@ def linear(x, w, *, splits: int = 0, status=None, out=None, scratch=None):
     return out
 
 
+MANY_ROWS = 512
+
+
+def many_rows(t: int) -> bool:
+    """Row counts from which the per-head products go to the library's batched GEMM (``ULC_PREFILL_GEMM=0``: never)."""
+    import os
+
+    return t >= MANY_ROWS and os.environ.get("ULC_PREFILL_GEMM", "1") != "0"
+
+
 def batched_linear(x, w, out):
     """For every batch index b: ``out[:, b, :] = x[:, b, :] @ w[b]^T`` on the tensor cores.
     ``x`` bf16 [T, batch, K] (any strides with unit inner stride, multiples of 8), ``w`` bf16
@@ -52,6 +62,15 @@ def batched_linear(x, w, out):
     T, Bt, K = x.shape
     N_ = w.shape[1]
     assert x.stride(2) == 1 and out.stride(2) == 1 and w.is_contiguous() and w.shape[0] == Bt and w.shape[2] == K
+    if many_rows(T):
+        # prefill-sized row counts: a plain batched bf16 GEMM, which the library does at several times the rate of
+        # the decode kernel (built for at most a few dozen rows per head); no epilogue is fused here
+        dst = out.permute(1, 0, 2)
+        if dst.is_contiguous():
+            torch.bmm(x.permute(1, 0, 2), w.transpose(1, 2), out=dst)
+        else:
+            out.copy_(torch.bmm(x.permute(1, 0, 2), w.transpose(1, 2)).permute(1, 0, 2))
+        return out
     code = N.cuda().ulc_gemm_wt_bf16_batched(
         N.ptr(x), N.ptr(w), N.ptr(out), C.c_int(T), C.c_int(N_), C.c_int(K), C.c_longlong(x.stride(0)),
         C.c_longlong(K), C.c_longlong(out.stride(0)), C.c_int(Bt), C.c_longlong(x.stride(1)),
@@ -75,6 +94,9 @@ def batched_linear_quant(x, w, *, status=None):
         y = torch.einsum("tbk,bnk->tbn", x.float(), w.float()).reshape(T, Bt * N_)
         return fp8.act_quant_reference(y)
     assert x.stride(2) == 1 and w.is_contiguous()
+    if many_rows(T):
+        y = torch.bmm(x.permute(1, 0, 2), w.transpose(1, 2)).permute(1, 0, 2).reshape(T, Bt * N_)
+        return fp8.act_quant(y)
     q = torch.empty((T, Bt * N_), dtype=torch.uint8, device=x.device)
     sc = torch.empty((T, Bt * N_ // 128), dtype=torch.float32, device=x.device)
     code = N.cuda().ulc_gemm_wt_bf16_batched_quant(
