@@ -238,3 +238,47 @@ def test_recorded_cohort_replays_check_order_positions_and_hash(tmp_path):
     assert logits.argmax(1).tolist() == [4, 9] and int(torch.isinf(logits).sum()) == 30
     with pytest.raises(ReplayMismatch):
         force_logits(torch.randn(1, 4), [[7]], [0])
+
+
+def test_received_index_records_are_published_to_their_owners_pages():
+    import numpy as np
+    import torch
+    from ulacache_b200.transfer.index_pages import (PAGE_BYTES, IndexRecordCopy, plan_index_record_copies,
+                                                    publish_index_record_bytes, publish_index_records, record_offsets,
+                                                    validate_index_record_plan)
+
+    ranks = 2
+    # logical records of pages 2..5 (pages 0-1 are the owners' padding pages); rank 1 owns pages 3 and 5
+    logical = [2 * 64 + 5, 3 * 64 + 0, 3 * 64 + 63, 5 * 64 + 7, 4 * 64 + 1]
+    received = [0, 1, 64, 65, 2]
+    plan = plan_index_record_copies(logical, received, ranks=ranks, rank=1)
+    assert [p.logical_record for p in plan] == [3 * 64, 3 * 64 + 63, 5 * 64 + 7]
+    assert [p.destination_record for p in plan] == [64, 127, 2 * 64 + 7]
+    assert record_offsets(65) == (PAGE_BYTES + 128, PAGE_BYTES + 8192 + 4)
+    rng = np.random.default_rng(0)
+    staging = rng.integers(0, 255, 2 * PAGE_BYTES, dtype=np.uint8)
+    canon = np.zeros(3 * PAGE_BYTES, dtype=np.uint8)
+    assert publish_index_record_bytes(staging, canon, plan, transport_quiesced=True) == 3
+    for p in plan:
+        assert np.array_equal(canon[p.destination_key_byte:p.destination_key_byte + 128], staging[p.source_key_byte:p.source_key_byte + 128])
+        assert np.array_equal(canon[p.destination_scale_byte:p.destination_scale_byte + 4], staging[p.source_scale_byte:p.source_scale_byte + 4])
+    assert int((canon != 0).sum()) <= 3 * 132
+    # the tensor form writes the same bytes
+    canon_t = torch.zeros(3, PAGE_BYTES, dtype=torch.uint8)
+    assert publish_index_records(torch.from_numpy(staging).view(2, PAGE_BYTES), canon_t, plan, transport_quiesced=True) == 3
+    assert np.array_equal(canon_t.numpy().reshape(-1), canon)
+    with pytest.raises(RuntimeError):
+        publish_index_record_bytes(staging, canon, plan, transport_quiesced=False)
+    with pytest.raises(ValueError):
+        publish_index_record_bytes(canon, canon, plan, transport_quiesced=True)            # aliasing
+    with pytest.raises(ValueError):
+        publish_index_record_bytes(staging, canon[: 2 * PAGE_BYTES].copy(), plan, transport_quiesced=True)   # beyond storage
+    with pytest.raises(ValueError):
+        plan_index_record_copies([5], [0], ranks=2, rank=0)                                 # padding page
+    with pytest.raises(ValueError):
+        plan_index_record_copies([200, 200], [0, 1], ranks=2, rank=0)                       # duplicates
+    with pytest.raises(ValueError):
+        IndexRecordCopy(2, 0, 3 * 64, 0, 64, 0, 0, 8192, 8192)                              # page 3 belongs to rank 1
+    dup = plan + (plan[0],)
+    with pytest.raises(ValueError):
+        validate_index_record_plan(dup, 2 * PAGE_BYTES, 3 * PAGE_BYTES)
