@@ -69,3 +69,81 @@ def test_execution_lifecycle_enforces_order():
                        "finish_layer_attention", "finish_model_forward"]
     ex.begin(); ex.abort()
     assert c.calls[-1] == "abort_model_forward"
+
+
+def test_shared_selection_lifecycle_orders_plans_pulls_and_joins():
+    import pytest
+    from ulacache_b200.cache.layers import LayerReuseSpecification
+    from ulacache_b200.cache.prefetch import SharedSelectionLifecycle
+    from ulacache_b200.cache_config import PrefetchPolicy
+    from ulacache_b200.transfer.prefill_pipeline import HostStreamRuntime
+
+    groups = LayerReuseSpecification.from_layer_groups(5, selection_groups=((0, 1, 2), (3, 4))).residency_groups()
+    calls = []
+    published = []
+
+    def make(prefetch, rt=None):
+        calls.clear()
+        return SharedSelectionLifecycle(groups, plan_selection=lambda l, s: calls.append(("plan", l)),
+                                        pull_history=lambda l, a: calls.append(("pull", l, a)),
+                                        publish_step=lambda: published.append(1), prefetch=prefetch, runtime=rt)
+
+    def forward(life):
+        life.begin_forward()
+        for layer in range(5):
+            life.before_layer_prepare(layer)
+            if layer in groups.anchors:
+                life.on_selection_ready(layer, object())
+            life.before_history_consume(layer)
+            life.after_attention(layer)
+        life.finish_forward()
+
+    # without prefetch: plan at the anchor, every layer pulls just before it reads
+    life = make(False)
+    forward(life)
+    assert calls == [("plan", 0), ("pull", 0, True), ("pull", 1, False), ("pull", 2, False), ("plan", 3),
+                     ("pull", 3, True), ("pull", 4, False)]
+    assert published == [1] and life.plans == 2 and life.pulls == 5 and not life.in_forward
+
+    # with prefetch, one event per follower layer: the anchor's pull follows its plan at once, the followers'
+    # pulls are queued when the anchor's attention has been launched, every follower joins its own event
+    rt = HostStreamRuntime()
+    life = make(PrefetchPolicy(enabled=True, completion="layer"), rt)
+    forward(life)
+    assert calls == [("plan", 0), ("pull", 0, True), ("pull", 1, False), ("pull", 2, False), ("plan", 3),
+                     ("pull", 3, True), ("pull", 4, False)]
+    ev1 = life._layer_ready[1]
+    rec = [i for i, e in enumerate(rt.log) if e[:2] == ("record", ev1)]
+    wait = [i for i, e in enumerate(rt.log) if e[:1] == ("wait_event",) and e[2] == ev1]
+    assert rec and wait and rec[0] < wait[0]
+    assert sum(1 for e in rt.log if e[0] == "wait_event") == 2 + 3     # two anchors, three followers
+
+    # one event per group: only the first follower joins
+    rt = HostStreamRuntime()
+    life = make(PrefetchPolicy(enabled=True, completion="group"), rt)
+    forward(life)
+    assert sum(1 for e in rt.log if e[0] == "wait_event") == 2 + 2
+
+    # misuse is refused
+    life = make(True, HostStreamRuntime())
+    life.begin_forward()
+    with pytest.raises(RuntimeError):
+        life.begin_forward()
+    with pytest.raises(RuntimeError):
+        life.join_idle_prefetch()
+    with pytest.raises(RuntimeError):
+        life.before_history_consume(0)                     # no plan yet
+    with pytest.raises(RuntimeError):
+        life.on_selection_ready(1, object())               # not an anchor
+    life.on_selection_ready(0, object())
+    with pytest.raises(RuntimeError):
+        life.on_selection_ready(0, object())               # planned twice
+    with pytest.raises(RuntimeError):
+        life.before_layer_prepare(1)                       # follower not scheduled: the anchor has not attended
+    with pytest.raises(RuntimeError):
+        life.finish_forward()                              # unconsumed layers
+    life.abort_forward()
+    assert not life.in_forward
+    life.join_idle_prefetch()
+    with pytest.raises(TypeError):
+        SharedSelectionLifecycle(groups, plan_selection=print, pull_history=print, prefetch="yes")
