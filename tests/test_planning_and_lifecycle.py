@@ -147,3 +147,85 @@ def test_shared_selection_lifecycle_orders_plans_pulls_and_joins():
     life.join_idle_prefetch()
     with pytest.raises(TypeError):
         SharedSelectionLifecycle(groups, plan_selection=print, pull_history=print, prefetch="yes")
+
+
+def test_framework_adapter_decode_prefill_reconstruction_and_pages():
+    import pytest
+    import torch
+    import ulacache_b200 as ula
+    from ulacache_b200.bindings import LocalCacheBindings
+    from ulacache_b200.cache.attention_access import FrameworkCacheExecution, LifecycleError, WriterStaging
+    from ulacache_b200.ops import records
+    from helpers import make_spec, random_kv
+
+    spec = make_spec(layers=3, device_pages=4, host_pages=16, queries=8, topk=32, shared_groups=((0, 1),))
+    import dataclasses
+
+    b = LocalCacheBindings(device="cpu")
+    b = dataclasses.replace(b, execution_options=dataclasses.replace(b.execution_options, record_storage_backend="native_paged"))
+    cache = ula.init(spec, b)
+    ids = cache.alloc(600)
+    latent, rope = random_kv(600, 4)
+    enc = records.encode_scaled656(latent, rope)
+    for layer in range(3):
+        cache.write(ids, layer, enc)
+    pos = {int(i): n for n, i in enumerate(ids.tolist())}
+    staging = WriterStaging()
+    fx = FrameworkCacheExecution(cache, 3, device="cpu", query_capacity=8, writer_staging=staging,
+                                 prefill_chunk_capacity=100)
+    with pytest.raises(LifecycleError):
+        fx.prepare_attention(0, ids[:8].reshape(2, 4))                 # no forward open
+
+    # ---- a decode-like forward: 3 real queries padded to 4, the writer staged 3 new records per layer ----
+    new = cache.alloc(3)
+    sel = torch.stack([ids[torch.randperm(600, generator=torch.Generator().manual_seed(q))[:32]] for q in range(4)]).to(torch.int32)
+    fx.begin_forward(decode_like=True, query_count=4)
+    for layer in range(3):
+        fresh = torch.full((3, 656), 50 + layer, dtype=torch.uint8)
+        staging.stage(layer, new, fresh)
+        rows = fx.prepare_attention(layer, sel.reshape(4, 1, 32))
+        assert rows.shape == (4, 1, 32) and bool((rows >= 0).all())
+        got = cache.gather_selected_records(layer).view(4, 32, 656)
+        assert torch.equal(got[0], enc[[pos[int(i)] for i in sel[0].tolist()]])
+        back = cache.engine.read_records(layer, new)[0]
+        assert bool((back == 50 + layer).all())                        # published after the transaction
+        fx.finish_attention(layer)
+    fx.finish()
+    assert staging.published_records == 9 and staging.pending_logical_record_ids(0) is None
+
+    # ---- an eager prefill forward through the engine's union ----
+    fx.begin_forward(decode_like=False, query_count=4)
+    staging.stage(2, new, torch.full((3, 656), 77, dtype=torch.uint8))
+    fx.publish_after_native_write(2)
+    assert bool((cache.engine.read_records(2, new)[0] == 77).all())
+    for layer in (0, 1, 2):
+        rows = fx.prepare_attention(layer, sel)
+        got = cache.engine.layer_plane(layer)[rows[1].long()]
+        assert torch.equal(got, enc[[pos[int(i)] for i in sel[1].tolist()]])
+        fx.finish_attention(layer)
+    fx.finish()
+
+    # ---- prefix reconstruction in chunks of 100 records ----
+    prefix = ids[100:350].to(torch.int32)
+    out = torch.zeros(250, 656, dtype=torch.uint8)
+    chunks = []
+
+    def read_native(planes, rows, dst):
+        chunks.append(int(rows.numel()))
+        dst.copy_(planes[0][rows.long()])
+
+    fx.reconstruct_prefill_records(1, prefix, out, read_native)
+    assert chunks == [100, 100, 50] and torch.equal(out, enc[100:350])
+
+    # ---- page-granular registration, clear, inventory ----
+    page = torch.tensor([int(ids.max()) // 64 + 2])
+    fx.register_full_pages(page, prefer_device=False)
+    assert cache.counters()["registered"] == 2 * (603 + 64)             # (counted once per residency group: two groups)
+    fx.release_full_pages(page)
+    assert cache.counters()["registered"] == 2 * 603
+    assert len(fx.get_device_storage_inventory()) >= 3
+    fx.clear_records()
+    assert cache.counters()["registered"] == 2 * 63                    # only the reserved records of the first page
+    with pytest.raises(ValueError):
+        fx.begin_forward(decode_like=True, query_count=9)
+    cache.close()
