@@ -229,3 +229,35 @@ def test_framework_adapter_decode_prefill_reconstruction_and_pages():
     with pytest.raises(ValueError):
         fx.begin_forward(decode_like=True, query_count=9)
     cache.close()
+
+
+def test_plan_details_owner_lowering_and_specification_checks():
+    import dataclasses
+    from ulacache_b200.cache.planning import lower_for_record_owners, validate_rank_local_specification
+    from ulacache_b200.cache.access import SparseAccessSpecification
+    from ulacache_b200.cache.specification import MemoryTierCapacity
+    from helpers import make_spec
+
+    spec = LayerReuseSpecification.from_layer_groups(6, key_value_groups=[(3, 4)], selection_groups=[(0, 1, 2), (3, 4)])
+    plan = lower_layer_reuse(spec)
+    assert plan.selection_producers == (0, 3, 5) and plan.selection_index_of_layer == (0, 0, 0, 1, 1, 2)
+    assert plan.last_consumer_of_selection == (2, 4, 5) and plan.step_reader_retirement_layer == 5
+    assert plan.bank_ranges_of_domain == (((0, 3),), ((3, 4),), ((4, 5),))
+    # record owners: one directory per KV bank; a selection shared by several banks is planned per bank
+    shared = LayerReuseSpecification.from_layer_groups(4, key_value_groups=[(2, 3)], selection_groups=[(0, 1, 2, 3)])
+    owner_plan = lower_for_record_owners(shared)
+    assert owner_plan.describe()["residency_domains"] == 3 and owner_plan.selection_producer == (0, 1, 2, 2)
+    assert owner_plan.step_reader_retirement_layer == 3
+
+    good = make_spec(layers=4, shared_groups=((0, 1),))
+    validate_rank_local_specification(good)
+    with pytest.raises(ValueError):
+        validate_rank_local_specification(dataclasses.replace(
+            good, capacity_plan=MemoryTierCapacity(device_record_capacity=100, host_record_capacity=64,
+                                                   maximum_write_record_count=64)))
+    with pytest.raises(NotImplementedError):
+        validate_rank_local_specification(dataclasses.replace(
+            good, sparse_access=SparseAccessSpecification(16, 8, selection_unit="block", records_per_selected_unit=16)))
+    with pytest.raises(NotImplementedError):                      # a selection shared across two directories
+        validate_rank_local_specification(dataclasses.replace(
+            good, layer_reuse=LayerReuseSpecification((0, 1, 2, 3), (0, 1, 2, 3), (0, 0, 2, 3), (0, 1, 2, 3))))

@@ -45,6 +45,20 @@ class PagedCacheExecutionPlan:
     index_bank_of_layer: Tuple[int, ...]
     domain_of_layer: Tuple[int, ...]
     workspace_count: int
+    selection_producers: Tuple[int, ...] = ()              # distinct producer layers, ascending
+    selection_index_of_layer: Tuple[int, ...] = ()
+    last_consumer_of_selection: Tuple[int, ...] = ()
+    bank_ranges_of_domain: Tuple[Tuple[Tuple[int, int], ...], ...] = ()   # contiguous [first, last + 1) bank runs
+
+    @property
+    def step_reader_retirement_layer(self):
+        """The layer after which ALL readers of a step can retire in one publication: the last consumer of any
+        selection, provided every directory serves one selection per forward (None otherwise: retire per
+        selection)."""
+        domains = tuple(self.domain_of_layer[l] for l in self.selection_producers)
+        if not domains or len(domains) != len(set(domains)):
+            return None
+        return max(self.last_consumer_of_selection)
 
     def is_anchor(self, layer: int) -> bool:
         return self.domains[self.domain_of_layer[layer]].anchor_layer == layer
@@ -80,5 +94,64 @@ def lower_layer_reuse(spec: LayerReuseSpecification) -> PagedCacheExecutionPlan:
     colours, n_colours = colour_workspaces(lifetimes)
     domains = tuple(ResidencyDomain(dom_idx[a], a, dom_layers[a], tuple(sorted({bank_of[l] for l in dom_layers[a]})),
                                     colours[i]) for i, a in enumerate(anchors))
+    producers = tuple(sorted(set(spec.sparse_selection_owners)))
+    sel_idx = {l: i for i, l in enumerate(producers)}
+    last = tuple(max(l for l, o in enumerate(spec.sparse_selection_owners) if o == pr) for pr in producers)
+    ranges = []
+    for d in domains:
+        runs = []
+        for b in d.banks:
+            if runs and runs[-1][1] == b:
+                runs[-1] = (runs[-1][0], b + 1)
+            else:
+                runs.append((b, b + 1))
+        ranges.append(tuple(runs))
     return PagedCacheExecutionPlan(banks, ibanks, domains, tuple(spec.sparse_selection_owners), bank_of, ibank_of,
-                                   tuple(dom_idx[a] for a in spec.residency_plan_anchors), n_colours)
+                                   tuple(dom_idx[a] for a in spec.residency_plan_anchors), n_colours, producers,
+                                   tuple(sel_idx[o] for o in spec.sparse_selection_owners), last, tuple(ranges))
+
+
+def lower_for_record_owners(spec: LayerReuseSpecification) -> PagedCacheExecutionPlan:
+    """Lowering for the record-owner engine: every KV bank gets its OWN directory and publication boundary.  A
+    selection shared across banks still names the same logical ids, but each bank plans its physical placement at
+    its first consumer, so the selection owner of a layer becomes the first layer that consumes the same
+    (bank, selection) pair; KV aliases stay in one bank.
+
+    Reference: ulacache/cache/planning.py:63-90 (create_owner_paged_execution_plan)."""
+    first = {}
+    owners = []
+    for layer, pair in enumerate(zip(spec.key_value_storage_owners, spec.sparse_selection_owners)):
+        first.setdefault(pair, layer)
+        owners.append(first[pair])
+    lowered = LayerReuseSpecification(spec.key_value_storage_owners, spec.index_storage_owners, tuple(owners),
+                                      spec.key_value_storage_owners)
+    return lower_layer_reuse(lowered)
+
+
+def validate_rank_local_specification(cache_specification) -> None:
+    """Everything a rank-local engine cannot lower, refused before any memory is allocated: selections that do
+    not name logical records, device capacity that is not page aligned, logical ids beyond int32, a shared KV
+    bank or a shared selection that spans two directories.
+
+    Reference: ulacache/cache/planning.py:92-186 (checks of create_paged_cache_execution_plan), :188-246
+    (create_rank_local_layer_groups)."""
+    reuse = cache_specification.layer_reuse
+    access = cache_specification.sparse_access
+    cap = cache_specification.capacity_plan
+    layout = cache_specification.storage_layout
+    if access.selection_unit != "record" or access.selection_identifier_space != "logical":
+        raise NotImplementedError("selections must name canonical logical records")
+    if cap.device_record_capacity % 64:
+        raise ValueError("device record capacity must be a multiple of the 64-record page")
+    if cap.logical_record_capacity >= 2 ** 31:
+        raise ValueError("logical record ids must fit positive int32")
+    for plane in layout.record_planes:
+        if plane.bytes_per_record % 4:
+            raise ValueError("records are multiples of 4 bytes")
+    for layer, owner in enumerate(reuse.key_value_storage_owners):
+        if reuse.residency_plan_anchors[layer] != reuse.residency_plan_anchors[owner]:
+            raise NotImplementedError("a shared KV bank needs one residency directory")
+    for layer, producer in enumerate(reuse.sparse_selection_owners):
+        if reuse.residency_plan_anchors[layer] != reuse.residency_plan_anchors[producer]:
+            raise NotImplementedError("a shared selection needs one residency directory")
+    lower_layer_reuse(reuse)      # (also rejects a directory that would serve two selections in one forward)
