@@ -261,3 +261,46 @@ def test_plan_details_owner_lowering_and_specification_checks():
     with pytest.raises(NotImplementedError):                      # a selection shared across two directories
         validate_rank_local_specification(dataclasses.replace(
             good, layer_reuse=LayerReuseSpecification((0, 1, 2, 3), (0, 1, 2, 3), (0, 0, 2, 3), (0, 1, 2, 3))))
+
+
+def test_position_sharded_engine_bounds_buffers_and_inventory():
+    import torch
+    import ulacache_b200 as ula
+    from ulacache_b200.bindings import PositionShardBindings
+    from ulacache_b200.cache.access import SparseAttentionAccessPlan
+    from ulacache_b200.storage.layout import PositionShardLayout
+    from helpers import make_spec
+
+    spec = make_spec(layers=2, device_pages=4, host_pages=16, queries=4, topk=32)
+    cache = ula.init(spec, PositionShardBindings(device="cpu", position_layout=PositionShardLayout(2), rank=1))
+    eng = cache.engine
+    ids = cache.alloc(400)
+    sel = ids[torch.arange(4 * 32).reshape(4, 32)].to(torch.int32)
+    cur = ids[300:304].to(torch.int32)
+    cache.begin_model_forward()
+    buf = eng.selected.data_ptr()
+    eng.plan(0, SparseAttentionAccessPlan(sel, cur))
+    counts = eng.selected_counts(0)
+    assert counts.tolist() == [int(((sel[q] % 2) == 1).sum()) for q in range(4)]
+    assert eng.selected.data_ptr() == buf and eng.selected_counts(0).data_ptr() == eng.selected_count[0].data_ptr()
+    mapped = eng._map_current(cur)                                # cached by the identity of the tensor
+    assert mapped.tolist() == [int(i) // 2 if int(i) % 2 == 1 else -1 for i in cur.tolist()]
+    eng.current[:4] = 123
+    assert eng._map_current(cur).tolist() == [123] * 4           # same tensor: not recomputed
+    eng.after_attention(0)
+    cache.finish_model_forward()
+    assert eng._current_signature is None
+    cache.begin_model_forward()
+    with pytest.raises(ValueError):
+        eng.plan(0, SparseAttentionAccessPlan(torch.ones(5, 32, dtype=torch.int32), None))   # too many queries
+    with pytest.raises(ValueError):
+        eng.plan(0, SparseAttentionAccessPlan(sel, cur[:3]))                                  # current per query
+    cache.abort_model_forward()
+    with pytest.raises(NotImplementedError):
+        eng.allocate_receive_rows(ids[:4])
+    with pytest.raises(NotImplementedError):
+        eng.plan_prefill(0, sel)
+    inv = eng.memory_inventory()
+    assert inv["record_distribution"] == "position_modulo_cp" and inv["storage_owner_count"] == 2
+    assert inv["additional_mapping_bytes"] == (2 * 4 * 32 + 2 * 4 + 4) * 4 and len(eng.device_storage_inventory()) >= 3
+    cache.close()
