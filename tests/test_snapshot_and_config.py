@@ -117,6 +117,17 @@ def test_snapshot_round_trip(tmp_path):
             if c is cache:
                 want = rows
         assert torch.equal(rows, want)
+    # a part of the bank, read back through the cache after every chunk; the page tail of the allocation is released
+    part = ula.init(spec, LocalCacheBindings(device="cpu"))
+    part_ids = part.alloc(192)                                   # three pages for a history of 150 + 1 tokens
+    assert cache_io.restore(part, path, {"b": part_ids}, verify_restored=True) == 2 * 150
+    before = part.counters()["registered"]
+    assert cache_io.release_unwritten_padding(part, part_ids, 150) == 42
+    assert part.counters()["registered"] == before - 2 * 42     # (counted once per residency group)
+    with pytest.raises(ValueError):
+        cache_io.restore(part, path, {"c": part_ids})            # not a request of this bank
+    with pytest.raises(ValueError):
+        cache_io.release_unwritten_padding(part, part_ids, 0)
     # corrupt one byte: verification must fail
     f = os.path.join(path, "owner_000", "request_00000.mla_000.bin")
     raw = bytearray(open(f, "rb").read())

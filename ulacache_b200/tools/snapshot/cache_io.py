@@ -55,10 +55,32 @@ def save_shard(cache, path: str, layout: SnapshotLayout, requests: Sequence[Snap
     return writer.finish()
 
 
-def restore(cache, path: str, request_ids: Dict[str, object], *, verify_payload=None, index_writer=None) -> int:
-    """Write every snapshot record back into ``cache`` under the given logical IDs.  Returns records written
-    (counting each (layer, token) once per reading rank)."""
+def release_unwritten_padding(cache, allocated_ids, history_length: int):
+    """A restored request was given whole pages of ids; only its real history is bound to records.  The ids of the
+    page tail are released again, so that ordinary decode registers each later token exactly once when it is
+    written (a speculative caller, which reserves whole pages on purpose, does not call this).
+
+    Reference: ulacache/tools/snapshot/cuda.py:12-27 (release_unwritten_padding)."""
+    n = int(allocated_ids.numel())
+    if not 0 < history_length <= n:
+        raise ValueError("the real history must fit the allocation")
+    tail = allocated_ids[history_length:]
+    if tail.numel():
+        cache.release_logical_records(tail)
+    return int(tail.numel())
+
+
+def restore(cache, path: str, request_ids: Dict[str, object], *, verify_payload=None, index_writer=None,
+            verify_restored: bool = False) -> int:
+    """Write snapshot records back into ``cache`` under the given logical IDs: every saved request, or only those
+    named in ``request_ids`` (a subset restores part of a bank).  ``verify_restored``: read every restored chunk back
+    through the cache and compare it with the file's bytes.  Returns records written (counting each (layer, token)
+    once per reading rank).  Nothing is published to a request table or prefix tree here: the caller does that
+    after every owner's restore has succeeded."""
     reader = SnapshotReader(path, verify_payload=verify_payload)
+    saved = {r.key for r in reader.requests}
+    if not request_ids or not set(request_ids) <= saved:
+        raise ValueError("restore needs fresh ids for requests the snapshot holds")
     lay = reader.layout
     plane0 = cache.cache_specification.storage_layout.record_planes[0]
     if lay.kv_format != plane0.native_encoding or lay.mla_row_bytes != plane0.bytes_per_record:
@@ -67,6 +89,8 @@ def restore(cache, path: str, request_ids: Dict[str, object], *, verify_payload=
     with QuiescentRecordIO(cache):
         for owner in range(lay.owners):
             for req in reader.requests:
+                if req.key not in request_ids:
+                    continue
                 ids = request_ids[req.key][: req.next_position][owner::lay.owners]
                 if ids.numel() == 0:
                     continue
@@ -80,6 +104,8 @@ def restore(cache, path: str, request_ids: Dict[str, object], *, verify_payload=
                     src = FileRecordSource(reader.plane_file(owner, req.key, plane), 0, rows, lay.mla_row_bytes,
                                            lay.kv_format)
                     done += cache.write(ids, layer, src)
+                    if verify_restored:
+                        _verify_restored(cache, layer, ids, reader, owner, req.key, plane, lay.mla_row_bytes)
                 for layer in lay.index_anchors:
                     if index_writer is None:
                         continue
@@ -87,6 +113,20 @@ def restore(cache, path: str, request_ids: Dict[str, object], *, verify_payload=
                     data = b"".join(reader.iter_plane(owner, req.key, plane))
                     index_writer(layer, ids, data)
     return done
+
+
+def _verify_restored(cache, layer, ids, reader, owner, key, plane, row_bytes):
+    import torch
+
+    at = 0
+    for raw in reader.iter_plane(owner, key, plane, chunk_bytes=max(row_bytes, (4 << 20) // row_bytes * row_bytes)):
+        want = torch.frombuffer(bytearray(raw), dtype=torch.uint8).reshape(-1, row_bytes)
+        got = cache.engine.read_records(layer, ids[at:at + want.shape[0]])[0].cpu()
+        if not torch.equal(got, want):
+            raise ValueError(f"restored bytes of request {key}, {plane} differ from the snapshot")
+        at += want.shape[0]
+    if at != ids.numel():
+        raise ValueError("restored row count differs from the snapshot")
 
 
 def read_index_records(index_pool_layer, ids, *, page_tokens: int = 64, segment_bytes=(128, 4)):
