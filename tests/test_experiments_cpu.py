@@ -39,3 +39,39 @@ def test_serving_trace_shape():
     first = [r for r in tr if r["session"] == 0]
     assert first[1]["prompt"][: len(first[0]["prompt"])] == first[0]["prompt"]            # turns extend their history
     assert all(r["prompt"][:128] == tr[0]["prompt"][:128] for r in tr)                     # shared system prefix
+
+
+def test_frozen_workloads_are_reproducible_and_hash_pinned(tmp_path):
+    import pytest
+    from ulacache_b200.experiments import workloads as W
+
+    a, b = str(tmp_path / "a.jsonl.gz"), str(tmp_path / "b.jsonl.gz")
+    assert W.main(["prepare-conversations", a, "--sessions", "6", "--turns", "2,3", "--system-prefix", "128"]) == 0
+    assert W.main(["prepare-conversations", b, "--sessions", "6", "--turns", "2,3", "--system-prefix", "128"]) == 0
+    assert open(a, "rb").read() == open(b, "rb").read()                     # same seed, same bytes
+    wl = W.load_workload(a)
+    digest = wl["manifest"]["payload_sha256"]
+    assert W.load_workload(b, digest)["manifest"]["records"] == len(wl["records"])
+    with pytest.raises(ValueError):
+        W.load_workload(a, "0" * 64)
+    trace = W.as_trace(wl, vocab=1000)
+    by_session = {}
+    for r in trace:
+        by_session.setdefault(r["session"], []).append(r)
+    first = [v[0]["prompt"] for v in by_session.values()]
+    assert all(p[:128] == first[0][:128] for p in first)                    # one shared system prefix
+    for reqs in by_session.values():                                        # every turn extends the previous history
+        for prev, nxt in zip(reqs, reqs[1:]):
+            assert nxt["prompt"][: len(prev["prompt"])] == prev["prompt"] and len(nxt["prompt"]) > len(prev["prompt"]) + prev["max_new"]
+    assert max(max(r["prompt"]) for r in trace) < 1000 and [r["arrival"] for r in trace] == sorted(r["arrival"] for r in trace)
+    # a tampered payload is refused
+    import gzip
+    raw = gzip.decompress(open(a, "rb").read()).replace(b'"max_new":', b'"max_new": ', 1)
+    open(a, "wb").write(gzip.compress(raw, mtime=0))
+    with pytest.raises(ValueError):
+        W.load_workload(a)
+    docs = str(tmp_path / "docs.jsonl.gz")
+    assert W.main(["prepare-documents", docs, "--count", "200", "--mean-tokens", "98000"]) == 0
+    s = W.summary(W.load_workload(docs))
+    assert s["records"] == 200 and 80000 < s["prompt_tokens_mean"] < 120000 and s["prompt_tokens_max"] <= 262144
+    assert len(W.expand_prompt(W.load_workload(docs)["records"][0])) == W.load_workload(docs)["records"][0]["prompt_tokens"]

@@ -120,6 +120,9 @@ def main():
     ap.add_argument("--prefill-chunk", type=int, default=512)
     ap.add_argument("--device-records", type=int, default=32768)
     ap.add_argument("--host-multiple", type=float, default=2.0, help="host tier size as a multiple of the device tier")
+    ap.add_argument("--workload", default="", help="replay a frozen workload file (experiments/workloads.py) instead of a generated trace")
+    ap.add_argument("--workload-sha256", default=None, help="refuse the workload unless its payload has this hash")
+    ap.add_argument("--workload-limit", type=int, default=0, help="serve only the first N requests of the workload")
     ap.add_argument("--ttft-prompt", type=int, default=0,
                     help="instead of the replay: time to first token of ONE request with this many prompt tokens")
     ap.add_argument("--sections", type=int, default=0,
@@ -131,9 +134,17 @@ def main():
     cfg = DsaMoeConfig().tiny(layers=args.layers, topk=256) if args.tiny else DsaMoeConfig(layers=args.layers, unique_layer_weights=min(args.layers, 4))
     tl, th = (int(x) for x in args.turns.split(","))
     ol, oh = (int(x) for x in args.output.split(","))
-    trace = build_trace(sessions=args.sessions, turns_lo=tl, turns_hi=th, system_prefix=args.system_prefix,
-                        median_input=args.median_input, sigma=args.sigma, input_cap=args.input_cap, out_lo=ol, out_hi=oh,
-                        rate=args.rate, vocab=cfg.vocab)
+    workload_hash = None
+    if args.workload:
+        from .workloads import as_trace, load_workload
+
+        wl = load_workload(args.workload, args.workload_sha256)
+        workload_hash = wl["manifest"]["payload_sha256"]
+        trace = as_trace(wl, vocab=cfg.vocab, limit=args.workload_limit or None)
+    else:
+        trace = build_trace(sessions=args.sessions, turns_lo=tl, turns_hi=th, system_prefix=args.system_prefix,
+                            median_input=args.median_input, sigma=args.sigma, input_cap=args.input_cap, out_lo=ol, out_hi=oh,
+                            rate=args.rate, vocab=cfg.vocab)
     longest = max(len(r["prompt"]) + r["max_new"] for r in trace)
     import os
     import time
@@ -192,7 +203,9 @@ def main():
                    output_tokens_per_s=sum(e["out_tokens"] for e in every) / wall,
                    decode_steps=max(e["report"]["decode_steps"] for e in every), ranks=world,
                    padding_steps_rank0=srv.stats.get("padding_steps", 0))
-    rep.update(experiment="online_serving", requests=len(trace), sessions=args.sessions, layers=cfg.layers,
+    if workload_hash is not None:
+        rep["workload_sha256"] = workload_hash
+    rep.update(experiment="online_serving", requests=len(trace), sessions=len({r["session"] for r in trace}), layers=cfg.layers,
                device_records=args.device_records, host_records=int(args.device_records * args.host_multiple),
                total_prompt_tokens=sum(len(r["prompt"]) for r in trace), engine_steps=steps)
     if rank == 0:
