@@ -72,10 +72,12 @@ class NativePagedResidency(CacheEngine):
         super().begin_forward(context)
         self._prefill_planned.clear()
 
-    def allocate_receive_rows(self, ids):
+    def allocate_receive_rows(self, ids, *, order_free_tail: bool = True):
         """Register ``ids`` in the HOST tier without publishing payloads and return their host rows
         (int64 [n]): the receiver writes ``layer_host_plane(layer)[rows]`` and the records become
-        readable with the next residency transaction."""
+        readable with the next residency transaction.  ``order_free_tail``: first sort the top of the free
+        stack, so that the rows come out ascending and mostly adjacent and a transport can write them as a few
+        contiguous extents."""
         import torch
 
         self.require_idle("binding receive rows")
@@ -83,6 +85,8 @@ class NativePagedResidency(CacheEngine):
             raise RuntimeError("receive rows live in the host tier, which this cache was built without")
         flat = ids.reshape(-1)
         for res in self.residency:
+            if order_free_tail:
+                res.order_host_free_tail(int(flat.numel()))
             res.register(flat, prefer_device=False)
         res = self.residency[0]
         mine, local = res._owned_locals(flat.to(torch.int32).to(res.directory.device))

@@ -97,6 +97,15 @@ class _ResidencyBase:
     def metadata_bytes(self) -> int:
         return sum(getattr(self, k).numel() * 4 for k in self.STATE)
 
+    def order_host_free_tail(self, records: int) -> bool:
+        """Before a receive of ``records`` records: sort the top of the host free stack so that the slots handed out
+        next are ascending and mostly adjacent (contiguous receive extents).  Only a bounded tail is permuted; the
+        set of free slots, the count and every live entry stay as they are.  Call between forwards, on the stream
+        that allocates."""
+        from ..ops import paired
+
+        return paired.sort_free_tail(self.host_free, self.counters[CNT_HOST_FREE:CNT_HOST_FREE + 1], records)
+
     def stats(self) -> dict:
         c = self.counters.tolist()
         return {"epoch": c[CNT_EPOCH], "hbm_free": c[CNT_HBM_FREE], "host_free": c[CNT_HOST_FREE],
