@@ -25,7 +25,6 @@ write_native_paged_records :655, device_storage_inventory :685, memory_inventory
 from __future__ import annotations
 
 from ..storage.layout import OwnerMap
-from .access import SparseAttentionAccessPlan
 from .engine import CacheEngine
 
 
