@@ -95,3 +95,27 @@ def test_fused_histogram_select_matches_separate_kernels(native, R, n_q, max_pag
         for r in range(R * n_q):
             assert sorted(got[r].tolist()) == sorted(want[r].tolist()), (trial, r)
         assert topk_op.workspace_is_clean(ws, R * n_q)         # the select leaves histograms and counters zero
+
+
+def test_prefill_sized_selection_with_explicit_lengths_matches_the_fused_pair(native):
+    """96 rows of growing context (a prefill chunk): plain scores + the row-parallel select given each row's
+    length pick the records the score epilogue's histograms + the select that starts from them pick."""
+    from ulacache_b200.ops import topk as topk_op
+
+    torch.manual_seed(11)
+    pages, R, max_pages, k = 2048, 96, 150, 2048
+    pool = _index_pool(pages, 1)
+    q8, wf = indexer.quantize_queries(torch.randn(R, 1, 64, 128, device="cuda"), torch.rand(R, 1, 64, device="cuda"))
+    page_table = torch.stack([torch.randperm(pages, device="cuda")[:max_pages] for _ in range(R)]).to(torch.int32)
+    lengths = (torch.arange(R, device="cuda", dtype=torch.int32) * 97 + 5).clamp(max=max_pages * 64)
+    lengths[3], lengths[4], lengths[5] = 2048, 2049, 1
+    ws = topk_op.workspace(R, "cuda")
+    fused_logits = indexer.index_score(q8, wf, page_table, lengths, pool, topk_workspace=ws)
+    fused = indexer.select_topk(fused_logits, k, page_table, n_q=1, hist_workspace=ws)
+    plain_logits = indexer.index_score(q8, wf, page_table, lengths, pool)
+    rows = indexer.select_topk(plain_logits, k, page_table, n_q=1, lengths=lengths)
+    torch.cuda.synchronize()
+    for r in range(R):
+        a = sorted(i for i in fused[r].tolist() if i >= 0)
+        b = sorted(i for i in rows[r].tolist() if i >= 0)
+        assert a == b and len(a) == min(k, int(lengths[r])), r

@@ -409,6 +409,7 @@ class DsaMoeModel:
         # The index-score kernel leaves each row's score histogram in this workspace and the radix
         # select starts from it (ULC_TOPK_FUSED=0: separate score and select kernels, for comparison).
         self._topk_ws = None
+        self._topk_rows = _os.environ.get("ULC_TOPK_ROWS", "1") == "1"      # (0: the histogram pair at every row count)
         if self.device.type == "cuda" and _os.environ.get("ULC_TOPK_FUSED", "1") == "1":
             from ..ops import topk as _topk
 
@@ -603,11 +604,15 @@ class DsaMoeModel:
                                 gamma=w.index_gamma, beta=w.index_beta, cos_sin=self.cos_sin,
                                 positions=batch.lengths, owner_only=True, status=self.status)
         self._mark("index.score")
+        # prefill-sized row counts: plain scores, then the row-parallel select with explicit lengths (the histogram
+        # epilogue and the select that starts from it are built for a few dozen rows)
+        many = self._topk_rows and B >= 48 and self.kv_ranks == 1
+        ws = None if many else self._topk_ws
         logits = indexer.index_score(iq8, iwf, batch.req_pages, self._ctx, self.index_pool[layer],
                                      ranks=self.kv_ranks, rank=self.kv_rank,
-                                     status=self.status, topk_workspace=self._topk_ws)
+                                     status=self.status, topk_workspace=ws)
         self._mark("index.topk")
-        sel = self._select(logits, batch)
+        sel = self._select(logits, batch, ws, self._ctx if many else None)
         if self.deterministic:
             sel = torch.sort(sel, dim=1, descending=True).values.contiguous()
         if self.record_selections is not None:
@@ -651,13 +656,13 @@ class DsaMoeModel:
         self._mark("comm")
         return self._all_reduce(out) if self.attn_tp > 1 else (out, 1, 0)
 
-    def _select(self, logits, batch: DecodeBatch):
+    def _select(self, logits, batch: DecodeBatch, hist_workspace=None, lengths=None):
         """Top-k over the (local shard of the) scores -> logical IDs [B, topk]."""
         from ..ops import indexer
 
         c = self.cfg
         if self.kv_ranks == 1:
-            return indexer.select_topk(logits, c.topk, batch.req_pages, n_q=1, hist_workspace=self._topk_ws)
+            return indexer.select_topk(logits, c.topk, batch.req_pages, n_q=1, hist_workspace=hist_workspace, lengths=lengths)
         return self._distributed_select(logits, batch)
 
     def _distributed_select(self, logits, batch: DecodeBatch):

@@ -93,17 +93,17 @@ def cols_to_ids(cols, page_table, *, n_q, ranks, rank, out=None):
     return out
 
 
-def select_topk(logits, k, page_table, *, n_q, ranks=1, rank=0, with_values=False, hist_workspace=None):
+def select_topk(logits, k, page_table, *, n_q, ranks=1, rank=0, with_values=False, hist_workspace=None, lengths=None):
     """Local top-k of the score rows, translated to logical IDs (-1 where nothing valid).
-    ``hist_workspace``: see ``ops.topk.topk_paged_ids``."""
+    ``hist_workspace`` / ``lengths``: see ``ops.topk.topk_paged_ids``."""
     import torch
 
     if logits.is_cuda:
         vals = torch.empty((logits.shape[0], k), dtype=torch.float32, device=logits.device) if with_values else None
         ids = topk_op.topk_paged_ids(logits, k, page_table, rows_per_request=n_q, ranks=ranks, rank=rank, out_val=vals,
-                                     hist_workspace=hist_workspace)
+                                     hist_workspace=hist_workspace, lengths=lengths)
         return (ids, vals) if with_values else ids
-    cols = topk_op.topk_reference(logits, k)
+    cols = topk_op.topk_reference(logits, k, lengths)
     vals = torch.gather(logits, 1, cols.clamp(min=0).long())
     vals[cols < 0] = float("-inf")
     ids = cols_to_ids(cols, page_table, n_q=n_q, ranks=ranks, rank=rank)

@@ -103,12 +103,13 @@ def topk(scores, k, lengths=None, in_idx=None, xform=None, *, out=None, out_val=
 
 
 def topk_paged_ids(scores, k, pages, *, rows_per_request=1, ranks=1, rank=0, out=None, out_val=None,
-                   hist_workspace=None):
+                   hist_workspace=None, lengths=None):
     """Top-k of score rows whose columns are (allocation page * 64 + offset): emits logical record
     IDs ``((pages[v >> 6] * ranks + rank) << 6) | (v & 63)`` directly and -1 for -inf scores.
     ``hist_workspace``: the workspace the scoring kernel left the rows' histograms and valid lengths
     in (``ops.indexer.index_score(..., topk_workspace=...)``): selection then takes one launch that
-    reads each row's valid prefix only."""
+    reads each row's valid prefix only.  ``lengths`` (int32 per row, without a workspace): valid columns of each
+    row, so that a short row is not searched over the whole table width."""
     import torch
 
     rows, L = scores.shape
@@ -123,7 +124,7 @@ def topk_paged_ids(scores, k, pages, *, rows_per_request=1, ranks=1, rank=0, out
         N.check(code, "topk")
         return out
     code = N.cuda().ulc_topk_ex(
-        N.ptr(scores), C.c_longlong(scores.stride(0)), C.c_void_p(0), C.c_int(rows), C.c_int(L), C.c_int(k),
+        N.ptr(scores), C.c_longlong(scores.stride(0)), N.ptr(lengths), C.c_int(rows), C.c_int(L), C.c_int(k),
         C.c_void_p(0), C.c_longlong(0), C.c_void_p(0), C.c_longlong(0), N.ptr(pages), C.c_longlong(pages.stride(0)),
         C.c_int(rows_per_request), C.c_int(ranks), C.c_int(rank), C.c_int(1), N.ptr(out), N.ptr(out_val),
         C.c_void_p(0), N.stream())
