@@ -263,7 +263,7 @@ def test_plan_details_owner_lowering_and_specification_checks():
             good, layer_reuse=LayerReuseSpecification((0, 1, 2, 3), (0, 1, 2, 3), (0, 0, 2, 3), (0, 1, 2, 3))))
 
 
-def test_position_sharded_engine_bounds_buffers_and_inventory():
+def _position_sharded_scenario(device):
     import torch
     import ulacache_b200 as ula
     from ulacache_b200.bindings import PositionShardBindings
@@ -272,11 +272,11 @@ def test_position_sharded_engine_bounds_buffers_and_inventory():
     from helpers import make_spec
 
     spec = make_spec(layers=2, device_pages=4, host_pages=16, queries=4, topk=32)
-    cache = ula.init(spec, PositionShardBindings(device="cpu", position_layout=PositionShardLayout(2), rank=1))
+    cache = ula.init(spec, PositionShardBindings(device=device, position_layout=PositionShardLayout(2), rank=1))
     eng = cache.engine
     ids = cache.alloc(400)
-    sel = ids[torch.arange(4 * 32).reshape(4, 32)].to(torch.int32)
-    cur = ids[300:304].to(torch.int32)
+    sel = ids[torch.arange(4 * 32).reshape(4, 32)].to(torch.int32).to(device)
+    cur = ids[300:304].to(torch.int32).to(device)
     cache.begin_model_forward()
     buf = eng.selected.data_ptr()
     eng.plan(0, SparseAttentionAccessPlan(sel, cur))
@@ -292,7 +292,7 @@ def test_position_sharded_engine_bounds_buffers_and_inventory():
     assert eng._current_signature is None
     cache.begin_model_forward()
     with pytest.raises(ValueError):
-        eng.plan(0, SparseAttentionAccessPlan(torch.ones(5, 32, dtype=torch.int32), None))   # too many queries
+        eng.plan(0, SparseAttentionAccessPlan(torch.ones(5, 32, dtype=torch.int32, device=device), None))   # too many queries
     with pytest.raises(ValueError):
         eng.plan(0, SparseAttentionAccessPlan(sel, cur[:3]))                                  # current per query
     cache.abort_model_forward()
@@ -303,4 +303,26 @@ def test_position_sharded_engine_bounds_buffers_and_inventory():
     inv = eng.memory_inventory()
     assert inv["record_distribution"] == "position_modulo_cp" and inv["storage_owner_count"] == 2
     assert inv["additional_mapping_bytes"] == (2 * 4 * 32 + 2 * 4 + 4) * 4 and len(eng.device_storage_inventory()) >= 3
+    # a full step through the public API: this rank's share of every selection resolves to its local rows
+    lat, rope = torch.randn(400, 512, device=device), torch.randn(400, 64, device=device)
+    cache.write(ids.to(device), 0, (lat, rope))
+    cache.begin_model_forward()
+    view = cache.access(sel, 0)
+    counts = eng.selected_counts(0)
+    loc = view.device_record_indices
+    for q in range(4):
+        c = int(counts[q])
+        assert bool((loc[q, :c] >= 0).all())
+    cache.finish_layer_attention(0)
+    cache.finish_model_forward()
+    cache.check("position-sharded step")
     cache.close()
+
+
+def test_position_sharded_engine_bounds_buffers_and_inventory():
+    _position_sharded_scenario("cpu")
+
+
+@pytest.mark.gpu
+def test_position_sharded_engine_on_the_gpu(native):
+    _position_sharded_scenario("cuda")
