@@ -43,7 +43,22 @@ def init_distributed():
     os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
     torch.cuda.set_device(local)
     if not dist.is_initialized():
-        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+        # The collective library prints its version banner on STDOUT while it creates its first communicator (at
+        # the VERSION debug level whatever NCCL_DEBUG_FILE says).  Programs that print a result line on stdout must
+        # not have it mixed in: file descriptor 1 points at stderr while the communicator comes up.
+        import sys
+
+        sys.stdout.flush()
+        saved = os.dup(1)
+        os.dup2(2, 1)
+        try:
+            dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+            dist.barrier()                     # the first collective: the communicator exists afterwards
+            torch.cuda.synchronize()
+        finally:
+            sys.stdout.flush()
+            os.dup2(saved, 1)
+            os.close(saved)
     cpu_group = dist.new_group(backend="gloo")
     return rank, world, local, dist.group.WORLD, cpu_group
 
