@@ -401,6 +401,8 @@ def main():
             "hbm_floor": {"bandwidth_gbs": hbm_gbs, "bandwidth_source": hbm_src,
                           "bytes_per_rank_step_gb": {k: round(v / 1e9, 2) for k, v in floor.items() if k != "experts_touched_per_layer"},
                           "experts_touched_per_layer_per_rank": round(floor["experts_touched_per_layer"], 1),
+                          "largest_group": max(((k, v) for k, v in floor.items()
+                                                if k not in ("total", "experts_touched_per_layer")), key=lambda kv: kv[1])[0],
                           "note": "weak scaling shrinks the expert bytes per rank with N, so compare ms_per_step with "
                                   "hbm_floor_ms at each N rather than tokens/s across N"},
             "clocks": clocks.summary(),
