@@ -282,3 +282,26 @@ def test_received_index_records_are_published_to_their_owners_pages():
     dup = plan + (plan[0],)
     with pytest.raises(ValueError):
         validate_index_record_plan(dup, 2 * PAGE_BYTES, 3 * PAGE_BYTES)
+
+
+def test_budget_and_fp8_loading_helpers():
+    import torch
+    from ulacache_b200.ops import fp8
+    from ulacache_b200.tools import benchmark_budget as B, fp8_loading as F
+
+    assert B.restored_cohort_metadata_tokens(requests=32, page_size=64) == 33 * 64
+    # 1M physical rows, 32 requests, a 32K prefill reserve: (1048576 - 32768) / (32 * 64) pages, minus one page, capped at 2^15
+    assert B.hot_buffer_rows(physical_rows=1 << 20, requests=32, prefill_rows=32768) == min((1015808 // 2048) * 64 - 64, 32768)
+    assert B.hot_buffer_rows(physical_rows=1 << 22, requests=8, prefill_rows=1000) == 32768          # rank limit
+    with pytest.raises(ValueError):
+        B.hot_buffer_rows(physical_rows=100000, requests=64, prefill_rows=32768)                     # below one selection
+    with pytest.raises(ValueError):
+        B.restored_cohort_metadata_tokens(requests=0)
+    x = torch.randn(5, 512)
+    q, s = fp8.act_quant_reference(x.to(torch.bfloat16))
+    back = F.dequantize_aligned_rows(q, s, (1, 128))
+    assert back.shape == (5, 512) and (back - x).abs().max() < 0.3
+    assert F.aligned_row_block_scales(q.view(torch.float8_e4m3fn), s, (1, 128))
+    assert not F.aligned_row_block_scales(q, s, (128, 128)) and not F.aligned_row_block_scales(q, s[:, :3], (1, 128))
+    with pytest.raises(ValueError):
+        F.dequantize_aligned_rows(q, s.double(), (1, 128))
