@@ -75,3 +75,15 @@ def test_frozen_workloads_are_reproducible_and_hash_pinned(tmp_path):
     s = W.summary(W.load_workload(docs))
     assert s["records"] == 200 and 80000 < s["prompt_tokens_mean"] < 120000 and s["prompt_tokens_max"] <= 262144
     assert len(W.expand_prompt(W.load_workload(docs)["records"][0])) == W.load_workload(docs)["records"][0]["prompt_tokens"]
+
+
+def test_results_csv_grows_rows_and_columns(tmp_path):
+    import csv
+    from ulacache_b200.utils import append_result_csv
+
+    path = str(tmp_path / "results.csv")
+    append_result_csv(path, {"experiment": "decode_sweep", "global_batch": 64, "tokens_per_s": 2467.0})
+    append_result_csv(path, {"experiment": "decode_sweep", "global_batch": 128, "tokens_per_s": 4495.0})
+    append_result_csv(path, {"experiment": "decode_sweep", "global_batch": 256, "tokens_per_s": 7627.0, "clocks": {"sm_mhz": 1965}})
+    rows = list(csv.DictReader(open(path, newline="")))
+    assert [r["global_batch"] for r in rows] == ["64", "128", "256"] and rows[0]["clocks"] == "" and "1965" in rows[2]["clocks"]

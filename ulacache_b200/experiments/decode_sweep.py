@@ -30,6 +30,7 @@ def main():
     ap.add_argument("--steps", type=int, default=8)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--layers", type=int, default=0, help="fewer layers for a quick look (not a valid benchmark)")
+    ap.add_argument("--csv", default="", help="also append every point to this results.csv")
     args = ap.parse_args()
     # whatever NCCL logs (its version banner at the VERSION and WARN levels, more at INFO) goes to stderr:
     # stdout carries the result line only
@@ -73,11 +74,16 @@ def main():
         mem = eng.memory_report()
         if rank == 0:
             gb = bpg * world
-            print(json.dumps({"experiment": "decode_sweep", "parallelism": f"{args.mode}{world}", "global_batch": gb,
-                              "prompt_len": args.prompt_len, "ms_per_step": round(float(ms) / args.steps, 3),
-                              "tokens_per_s": round(gb * args.steps / (float(ms) / 1e3), 1),
-                              "kv_records_per_rank": mem["kv_records_per_rank"], "layers": cfg.layers,
-                              "distinct_layer_weight_sets_resident": unique, "valid": not args.layers}), flush=True)
+            row = {"experiment": "decode_sweep", "parallelism": f"{args.mode}{world}", "global_batch": gb,
+                   "prompt_len": args.prompt_len, "ms_per_step": round(float(ms) / args.steps, 3),
+                   "tokens_per_s": round(gb * args.steps / (float(ms) / 1e3), 1),
+                   "kv_records_per_rank": mem["kv_records_per_rank"], "layers": cfg.layers,
+                   "distinct_layer_weight_sets_resident": unique, "valid": not args.layers}
+            print(json.dumps(row), flush=True)
+            if args.csv:
+                from ..utils import append_result_csv
+
+                append_result_csv(args.csv, row)
         eng.close()
         del eng
         torch.cuda.empty_cache()
