@@ -83,6 +83,72 @@ def capture_decode_trace(path: str, *, steps: int, batch: int, prompt_len: int, 
     return n
 
 
+def _sha256(path: str) -> str:
+    import hashlib
+
+    with open(path, "rb") as f:
+        return hashlib.sha256(f.read()).hexdigest()
+
+
+def validate_capture(path: str, *, expected_sha256: str = None, layers: int = None) -> dict:
+    """Checks of a captured trace (int32 triples step, layer, id) before any policy is replayed over it: the file
+    hashes to what the capture recorded, steps run from 0 without gaps, every step has every layer, ids are
+    positive.  Returns the receipt that goes beside the results.
+
+    Reference: scripts/7_5_scheduler/_runtime/validate_capture.py:19 (hash-pinned chunks, shape and positivity
+    checks, coverage of every forward)."""
+    import numpy as np
+
+    digest = _sha256(path)
+    if expected_sha256 is not None and digest != expected_sha256:
+        raise ValueError("the captured trace changed since it was recorded")
+    data = np.load(path)
+    if data.ndim != 2 or data.shape[1] != 3 or data.dtype != np.int32 or data.shape[0] == 0:
+        raise ValueError("a captured trace is a non-empty int32 array of (step, layer, id) triples")
+    steps, lays, ids = data[:, 0], data[:, 1], data[:, 2]
+    if int(ids.min()) <= 0:
+        raise ValueError("captured ids must be positive (padding does not belong in a trace)")
+    n_steps = int(steps.max()) + 1
+    seen_layers = sorted(set(int(x) for x in np.unique(lays)))
+    if layers is not None and seen_layers != list(range(layers)):
+        raise ValueError(f"the trace covers layers {seen_layers}, not 0..{layers - 1}")
+    pairs = set(zip(steps.tolist(), lays.tolist()))
+    missing = [(s_, l_) for s_ in range(n_steps) for l_ in seen_layers if (s_, l_) not in pairs]
+    if missing:
+        raise ValueError(f"the trace misses (step, layer) {missing[:4]} ...: not every forward was captured")
+    per = np.bincount(steps.astype(np.int64) * len(seen_layers) + np.searchsorted(seen_layers, lays))
+    return dict(path=path, sha256=digest, steps=n_steps, layers=len(seen_layers), triples=int(data.shape[0]),
+                ids_per_step_layer_min=int(per.min()), ids_per_step_layer_max=int(per.max()), id_max=int(ids.max()))
+
+
+def compose_rank_traces(paths, out_path: str, *, id_space_per_rank: int) -> dict:
+    """One larger shared-pool load out of independent per-rank captures: rank r's ids get the fixed offset
+    ``r * id_space_per_rank`` (identity inside a rank is preserved), steps are aligned at 0 and cut to the shortest
+    capture.  A construction from traces, not a capture of a bigger batch; the receipt names every source by hash.
+
+    Reference: scripts/7_5_scheduler/_runtime/trace_data.py:18 (rank-offset UIDs, hashed sources)."""
+    import numpy as np
+
+    parts, sources, n_steps = [], [], None
+    for rank, path in enumerate(paths):
+        rec = validate_capture(path)
+        data = np.load(path).astype(np.int64)
+        if int(data[:, 2].max()) >= id_space_per_rank:
+            raise ValueError(f"{path}: ids exceed the per-rank id space")
+        data[:, 2] += rank * id_space_per_rank
+        if data[:, 2].max() >= 2 ** 31:
+            raise ValueError("composed ids no longer fit int32")
+        n_steps = rec["steps"] if n_steps is None else min(n_steps, rec["steps"])
+        parts.append(data)
+        sources.append(dict(rank=rank, path=path, sha256=rec["sha256"], id_offset=rank * id_space_per_rank, steps=rec["steps"]))
+    both = np.concatenate([p[p[:, 0] < n_steps] for p in parts]).astype(np.int32)
+    order = np.lexsort((both[:, 1], both[:, 0]))
+    np.save(out_path, both[order])
+    final = out_path if out_path.endswith(".npy") else out_path + ".npy"
+    return dict(path=final, sha256=_sha256(final), steps=n_steps, ranks=len(parts), sources=sources,
+                construction="trace-driven composition of per-rank captures (not a capture at the larger batch)")
+
+
 def gpu_policy_timing(steps, capacity: int, id_space: int):
     """Replay ``steps`` (lists of distinct ids) through the device policies; CUDA events around each step."""
     import torch
@@ -145,7 +211,18 @@ def main():
     ap.add_argument("--capture-layers", type=int, default=4)
     ap.add_argument("--full-width", action="store_true", help="capture from the full-width model instead of the tiny one")
     ap.add_argument("--gpu-timing", action="store_true", help="also replay through the device policies with per-step timing")
+    ap.add_argument("--validate", default="", help="check a captured trace and print its receipt")
+    ap.add_argument("--compose", default="", help="comma-separated per-rank traces to compose into one load")
+    ap.add_argument("--compose-to", default="composed_trace.npy")
+    ap.add_argument("--id-space-per-rank", type=int, default=1 << 24)
     args = ap.parse_args()
+    if args.validate:
+        print(json.dumps({"experiment": "scheduler_study_validate", **validate_capture(args.validate)}))
+        return
+    if args.compose:
+        rec = compose_rank_traces(args.compose.split(","), args.compose_to, id_space_per_rank=args.id_space_per_rank)
+        print(json.dumps({"experiment": "scheduler_study_compose", **rec}))
+        args.trace = rec["path"]
     if args.capture:
         n = capture_decode_trace(args.capture_to, steps=args.capture, batch=args.capture_batch, prompt_len=args.capture_prompt,
                                  layers=args.capture_layers, tiny=not args.full_width)
