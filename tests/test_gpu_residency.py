@@ -172,3 +172,41 @@ def test_receive_leases_and_publication_on_the_device(native):
     torch.cuda.synchronize()
     res.check_status("release")
     assert int(leases.leases.sum()) == 0
+
+
+def test_staged_receive_window_publishes_from_pinned_memory(native):
+    """The window's pinned pages are read by the publication kernel through their mapped address; records land in
+    whichever tier holds them now, sidecar banks (kernel path at 128-byte rows, index copy at 132) by record id."""
+    from ulacache_b200.transfer.receive_window import StagedReceiveWindow
+
+    cache = ula.init(make_spec(device_pages=2, host_pages=8), LocalCacheBindings(device="cuda"))
+    window = StagedReceiveWindow(cache, record_capacity=512, copy_chunk_records=200)
+    assert window.pinned and window.staging.is_pinned()
+    wide = torch.zeros(4096, 128, dtype=torch.uint8, device="cuda")
+    odd = torch.zeros(4096, 132, dtype=torch.uint8, device="cuda")
+    window.add_sidecar("wide", [wide])
+    window.add_sidecar("odd", [odd])
+    n = 300
+    ids = cache.alloc(320)
+    window.reserve("room", ids, record_count=n)
+    latent, rope = random_kv(n, 3)
+    payload = [records.encode_scaled656(latent * (l + 1), rope) for l in range(2)]
+    src = window.staging_rows("room")
+    for l in range(2):
+        window.staging[l, src] = payload[l]
+    side = {k: torch.randint(0, 255, (n, w), dtype=torch.uint8) for k, w in (("wide", 128), ("odd", 132))}
+    for k, v in side.items():
+        window._sidecars[k]["storage"][0, src] = v
+    assert window.publish("room") == n
+    assert torch.equal(wide[ids[:n].long()].cpu(), side["wide"]) and torch.equal(odd[ids[:n].long()].cpu(), side["odd"])
+    truth = records.decode_scaled656(payload[1])
+    pick_pos = torch.randperm(n, generator=torch.Generator().manual_seed(0))[:64]
+    cache.begin_model_forward()
+    cache.access(ids[pick_pos.cuda()].view(1, 64), 1)
+    got = records.decode_scaled656(cache.gather_selected_records(1)).view(64, 576)
+    assert torch.equal(got.cpu(), truth[pick_pos])
+    cache.finish_layer_attention(1)
+    cache.finish_model_forward()
+    cache.check()
+    assert int(window.leases[0].leases.sum()) == 0
+    cache.close()
