@@ -210,3 +210,26 @@ def test_staged_receive_window_publishes_from_pinned_memory(native):
     cache.check()
     assert int(window.leases[0].leases.sum()) == 0
     cache.close()
+
+
+def test_file_restore_alternates_two_pinned_buffers(native, tmp_path):
+    """A hashed file source streams into a CUDA cache through two pinned buffers; every record reads back equal."""
+    import hashlib
+
+    from ulacache_b200.transfer.file_io import FileRecordSource, restore_file_records
+
+    cache = ula.init(make_spec(layers=1, device_pages=2, host_pages=8), LocalCacheBindings(device="cuda"))
+    n = 300
+    latent, rope = random_kv(n, 1)
+    payload = records.encode_scaled656(latent, rope)
+    raw = payload.numpy().tobytes()
+    path = tmp_path / "kv.bin"
+    path.write_bytes(raw)
+    ids = cache.alloc(320)[:n]
+    stats = {}
+    src = FileRecordSource(str(path), 0, n, 656, "mla_scaled656", sha256=hashlib.sha256(raw).hexdigest(), file_bytes=len(raw))
+    assert restore_file_records(cache.engine, 0, ids, src, chunk_bytes=656 * 64, statistics=stats) == n
+    assert stats["chunks_read"] == 5 and stats["payload_sha256_verified"] and stats["leased_buffers"] == 0
+    assert torch.equal(cache.engine.read_records(0, ids)[0].cpu(), payload)
+    cache.check()
+    cache.close()

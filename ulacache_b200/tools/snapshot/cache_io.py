@@ -97,12 +97,11 @@ def restore(cache, path: str, request_ids: Dict[str, object], *, verify_payload=
                 rows = reader.plane_rows(owner, req.key)
                 for layer in range(lay.layers):
                     plane = f"mla_{layer:03d}"
-                    if reader.verify_payload:
-                        reader.verify_plane(owner, req.key, plane)      # hash before any record reaches the cache
-                    else:
-                        reader.validate_owner(owner)
-                    src = FileRecordSource(reader.plane_file(owner, req.key, plane), 0, rows, lay.mla_row_bytes,
-                                           lay.kv_format)
+                    # bound to the receipt's size and hash: the file is read once, hashed while it streams, and a
+                    # mismatch raises out of the write (the caller frees the ids; nothing was published)
+                    src = FileRecordSource.from_snapshot(reader, req.key, plane, owner=owner)
+                    if src.record_count != rows:
+                        raise ValueError("snapshot plane and request geometry differ")
                     done += cache.write(ids, layer, src)
                     if verify_restored:
                         _verify_restored(cache, layer, ids, reader, owner, req.key, plane, lay.mla_row_bytes)
