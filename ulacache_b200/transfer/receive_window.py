@@ -210,8 +210,12 @@ class StagedReceiveWindow:
         if not isinstance(name, str) or not name or name in self._sidecars:
             raise ValueError("a sidecar needs a unique non-empty name")
         dests = list(destinations)
-        if not dests or any(d.ndim < 2 or not d.is_contiguous() or d.shape[0] < 1 or d.device != self.engine.device
-                            for d in dests):
+        want = self.engine.device             # may carry no index ("cuda"): compare the type, and the index if given
+
+        def elsewhere(d):
+            return d.device.type != want.type or (want.index is not None and d.device.index != want.index)
+
+        if not dests or any(d.ndim < 2 or not d.is_contiguous() or d.shape[0] < 1 or elsewhere(d) for d in dests):
             raise ValueError("sidecar destinations are contiguous [rows, ...] tensors on the cache's device")
         flat = [d.view(torch.uint8).reshape(d.shape[0], -1) for d in dests]
         width = flat[0].shape[1]
