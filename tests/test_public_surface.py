@@ -1,0 +1,123 @@
+"""The names a user of the reference imports from the package root, and the accounting behind them."""
+import pytest
+
+
+REFERENCE_ROOT_NAMES = """CacheLayout ResidentQueryLayout InterleavedRecordLayout NativePageLayout LayerGroupPlan
+RequestPagePool RecordSpec history_capacity KeyValueRecordPlane KeyValueStorageLayout LayerReuseSpecification
+SparseAccessSpecification SparseAttentionAccessPlan ResidentAttentionInputs ResidentView MemoryTierCapacity
+UnifiedCacheSpecification UlaCache UnifiedMemoryCache LocalCacheBindings CacheExecutionOptions ForwardExecutionContext
+RecordOwnerBindings TensorParallelCacheBindings PositionShardBindings PositionShardLayout LogicalSlotAllocator
+FileRecordSource PrefetchPolicy init RecordOwnerCapacity RequiredCachePartitionCapacity RequestNamespaceCapacityBounds
+calculate_addressable_history_capacity CacheMemoryUsage CacheMemoryBudget CacheCapacityPlan plan_cache_capacity""".split()
+
+
+def test_every_root_name_of_the_reference_resolves():
+    import ulacache_b200 as ula
+
+    for name in REFERENCE_ROOT_NAMES:
+        assert getattr(ula, name) is not None, name
+        assert name in ula.__all__
+    with pytest.raises(AttributeError):
+        ula.no_such_name
+
+
+def test_history_capacity_and_native_page_layout():
+    from ulacache_b200 import NativePageLayout, history_capacity
+    from ulacache_b200.storage.layout import INDEX_FP8, MLA_SCALED656
+
+    assert history_capacity(64, 2048, 1.0, 64) == 131072
+    assert history_capacity(3, 100, 1.01, 64) == 320                 # ceil(303) -> 5 pages, not 6
+    for bad in (dict(max_queries=0, topk=1, multiplier=1, page_size=1), dict(max_queries=1, topk=1, multiplier=0.5, page_size=1),
+                dict(max_queries=1 << 20, topk=2048, multiplier=1.0, page_size=64)):
+        with pytest.raises(ValueError):
+            history_capacity(**bad)
+    page = NativePageLayout(64, (128, 8), 16)                        # keys then scales, segment after segment
+    assert page.row_bytes == 136 and page.bytes_per_page == 64 * 136
+    assert page.byte_offset(0, 0) == 0 and page.byte_offset(1, 0) == 128
+    assert page.byte_offset(1, 130) == 64 * 128 + 8 + 2              # second segment of row 1
+    assert page.byte_offset(64, 5) == page.bytes_per_page + 5        # next page
+    with pytest.raises(IndexError):
+        page.byte_offset(0, 136)
+    with pytest.raises(ValueError):
+        NativePageLayout(64, (128, 4), 16)                           # 4-byte segment: not a transport unit
+    whole = NativePageLayout.of_plane(MLA_SCALED656)
+    assert whole.segment_bytes == (656,) and whole.byte_offset(3, 10) == MLA_SCALED656.record_offset(3) + 10
+    with pytest.raises(ValueError):
+        NativePageLayout.of_plane(INDEX_FP8)
+
+
+def test_storage_tier_fields_and_packed_record_spec():
+    from ulacache_b200 import KeyValueStorageLayout, RecordSpec
+    from ulacache_b200.storage.layout import MLA_SCALED656, KeyValueRecordPlane
+
+    tier = KeyValueStorageLayout(record_planes=(MLA_SCALED656,))
+    assert (tier.name, tier.tokens_per_record, tier.records_per_page, tier.bytes_per_record) == ("kv", 1, 64, 656)
+    assert tier.calculate_storage_bytes(0) == 0 and tier.calculate_storage_bytes(65) == 2 * 64 * 656
+    with pytest.raises(ValueError):
+        KeyValueStorageLayout(record_planes=(MLA_SCALED656,), tokens_per_record=4)       # token records stand for one token
+    with pytest.raises(ValueError):
+        KeyValueStorageLayout(record_planes=(MLA_SCALED656, KeyValueRecordPlane("x", (64,), "x", page_tokens=32)))
+    spec = RecordSpec(compression_ratio=4, indexed_layer_ids=(2, 3, 4, 7, 8), topk=2304, row_bytes=584,
+                      native_segment_bytes=(576, 8), index_layer_anchors=(2, 2, 4, 7, 7), page_storage_alignment=576)
+    assert spec.local_layer_count(0, 5) == 3 and spec.local_layer_count(5, 9) == 2
+    assert spec.local_layer_anchors(0, 5) == (0, 0, 2) and spec.local_layer_anchors(5, 9) == (0, 0)
+    with pytest.raises(ValueError):
+        spec.local_layer_anchors(3, 9)                                # layer 3's anchor (2) is in another stage
+    plane = spec.plane()
+    assert plane.segment_major and plane.bytes_per_record == 584 and plane.bytes_per_page % 576 == 0
+    packed = spec.storage_layout()
+    assert packed.record_kind == "compressed" and packed.tokens_per_record == 4
+    with pytest.raises(NotImplementedError):
+        RecordSpec(1, (0,), 2000, 584, (576, 8), (0,))
+    with pytest.raises(ValueError):
+        RecordSpec(1, (0, 1), 2048, 584, (576, 8), (0, 5))           # anchor is not an indexed layer
+
+
+def test_addressable_history_audit():
+    from ulacache_b200 import (RecordOwnerCapacity, RequestNamespaceCapacityBounds, RequiredCachePartitionCapacity,
+                               calculate_addressable_history_capacity)
+    from ulacache_b200.storage.capacity import addressable_tokens_per_owner
+    from ulacache_b200.storage.layout import MLA_SCALED656, StorageLayout
+
+    kv = StorageLayout(record_planes=(MLA_SCALED656,), name="kv")
+    c4 = StorageLayout(record_planes=(MLA_SCALED656,), name="c4", record_kind="compressed", tokens_per_record=4)
+    owners = tuple(RecordOwnerCapacity(r, 1000, 3000) for r in range(4))
+    parts = [
+        RequiredCachePartitionCapacity(0, "kv", kv, owners, reserved_logical_record_count=64),
+        # the compressed tier keeps a quarter of the records, twice replicated: replicas add bytes, not capacity
+        RequiredCachePartitionCapacity(0, "c4", c4, tuple(RecordOwnerCapacity(r, 500, 400, 2) for r in range(4)), 0),
+        RequiredCachePartitionCapacity(1, "kv", kv, owners[:1], 0),
+    ]
+    bounds = [RequestNamespaceCapacityBounds(0, 20000, 1 << 30), RequestNamespaceCapacityBounds(1, 1 << 30, 2500)]
+    audit = calculate_addressable_history_capacity(parts, bounds)
+    p = {(x["request_namespace_id"], x["partition_name"]): x for x in audit["required_partitions"]}
+    assert p[(0, "kv")]["usable_history_token_slots"] == 16000 - 64
+    assert p[(0, "c4")]["usable_history_token_slots"] == 3600 * 4
+    assert p[(0, "c4")]["physical_device_cold_record_slots"] == 4000 and p[(0, "c4")]["unique_device_cold_record_slots"] == 2000
+    n = {x["request_namespace_id"]: x for x in audit["request_namespaces"]}
+    assert n[0]["cold_storage_history_token_slots"] == 14400 and n[0]["usable_history_token_slots"] == 14400
+    assert n[1]["usable_history_token_slots"] == 2500                 # the address limit binds
+    assert audit["total_usable_history_token_slots"] == 16900
+    with pytest.raises(ValueError):
+        calculate_addressable_history_capacity(parts, bounds[:1])     # namespace 1 has partitions but no bounds
+    with pytest.raises(ValueError):
+        calculate_addressable_history_capacity([RequiredCachePartitionCapacity(0, "kv", kv, owners + owners[:1], 0)], bounds[:1])
+    with pytest.raises(ValueError):
+        calculate_addressable_history_capacity([RequiredCachePartitionCapacity(0, "kv", kv, owners, 10 ** 6)], bounds[:1])
+    assert addressable_tokens_per_owner(maximum_requests=256, maximum_context_tokens=131072, owners=8) == 256 * 131072 // 8
+    assert addressable_tokens_per_owner(maximum_requests=1 << 20, maximum_context_tokens=1 << 20, owners=8) == (2 ** 31 - 1) // 8 // 64 * 64
+
+
+def test_resident_query_layout_sizes_from_real_queries():
+    from ulacache_b200 import CacheLayout, ResidentQueryLayout
+
+    base = dict(layers=4, groups=2, record_bytes=656, slots_per_rank=64 * 100, topk=2048, pulled_record_cache=True)
+    padded = CacheLayout(max_queries=256, **base)
+    real = ResidentQueryLayout(max_queries=256, max_resident_queries=80, **base)
+    assert real.resident_query_capacity == 80 and ResidentQueryLayout(max_queries=256, **base).resident_query_capacity == 256
+    assert real.cache_rows * 256 == padded.cache_rows * 80 and real.selected_bytes < padded.selected_bytes
+    assert real.rows_per_layer % 64 == 0 and real.rows_per_layer >= real.cache_rows + 80
+    assert real.report()["total"] < padded.report()["total"]
+    for bad in (dict(max_queries=100), dict(max_queries=4096), dict(max_queries=64, max_resident_queries=65)):
+        with pytest.raises(ValueError):
+            ResidentQueryLayout(**{**base, **bad})

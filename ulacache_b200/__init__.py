@@ -34,6 +34,28 @@ _EXPORTS = {
     "BackendServices": "ulacache_b200.bindings",
     "load_model_configuration": "ulacache_b200.config.model_configuration",
     "FileRecordSource": "ulacache_b200.transfer.file_io",
+    "ResidentAttentionInputs": "ulacache_b200.cache.access",
+    "LayerGroupPlan": "ulacache_b200.cache.layers",
+    "RequestPagePool": "ulacache_b200.cache.request_pages",
+    "LogicalSlotAllocator": "ulacache_b200.bindings",
+    "KeyValueRecordPlane": "ulacache_b200.storage.layout",
+    "KeyValueStorageLayout": "ulacache_b200.storage.layout",
+    "StorageLayout": "ulacache_b200.storage.layout",
+    "NativePageLayout": "ulacache_b200.storage.layout",
+    "InterleavedRecordLayout": "ulacache_b200.storage.layout",
+    "PositionShardLayout": "ulacache_b200.storage.layout",
+    "history_capacity": "ulacache_b200.storage.layout",
+    "CacheLayout": "ulacache_b200.storage.workspace",
+    "ResidentQueryLayout": "ulacache_b200.storage.workspace",
+    "RecordSpec": "ulacache_b200.storage.layout",
+    "CacheMemoryUsage": "ulacache_b200.storage.capacity",
+    "CacheMemoryBudget": "ulacache_b200.storage.capacity",
+    "CacheCapacityPlan": "ulacache_b200.storage.capacity",
+    "plan_cache_capacity": "ulacache_b200.storage.capacity",
+    "RecordOwnerCapacity": "ulacache_b200.storage.capacity",
+    "RequiredCachePartitionCapacity": "ulacache_b200.storage.capacity",
+    "RequestNamespaceCapacityBounds": "ulacache_b200.storage.capacity",
+    "calculate_addressable_history_capacity": "ulacache_b200.storage.capacity",
 }
 
 __all__ = sorted(_EXPORTS) + ["__version__"]

@@ -7,6 +7,7 @@ first maximises the TOTAL number of tokens and then, at that total, the share he
 
 Reference: ulacache/storage/capacity.py (request_history_capacity :13,
 flowkv_cpu_pool_geometry :67, CacheMemoryUsage/Budget/Plan :90-157, plan_cache_capacity :205,
+RecordOwnerCapacity :303, RequiredCachePartitionCapacity :322, RequestNamespaceCapacityBounds :339,
 calculate_addressable_history_capacity :403, plan_position_capacity :531).
 """
 from __future__ import annotations
@@ -159,29 +160,107 @@ def simple_usage_model(*, record_bytes: int, layers: int, index_layers: int = 0,
     return measure
 
 
-@dataclass(frozen=True)
-class RequestNamespaceCapacityBounds:
-    """Limits that come from addressing, not memory: int32 logical IDs and page tables."""
+def addressable_tokens_per_owner(*, maximum_requests: int, maximum_context_tokens: int, owners: int = 1,
+                                 page_size: int = PAGE_TOKENS) -> int:
+    """The addressing limit, not a memory limit: int32 logical ids striped over ``owners``, and no more than
+    every request at its longest context; whole pages."""
+    if min(maximum_requests, maximum_context_tokens, owners, page_size) < 1:
+        raise ValueError("Namespace bounds must be positive")
+    id_limit = (2 ** 31 - 1) // owners
+    need = maximum_requests * maximum_context_tokens // owners
+    return min(id_limit, need) // page_size * page_size
 
-    maximum_requests: int
-    maximum_context_tokens: int
-    owners: int = 1
-    page_size: int = PAGE_TOKENS
+
+@dataclass(frozen=True)
+class RecordOwnerCapacity:
+    """Cold-record slots of one owner of a partition.  Owners hold disjoint records; ``physical_replica_count``
+    copies of an owner hold the same records (they cost memory, they add no capacity)."""
+
+    owner_rank: int
+    device_record_capacity: int
+    host_record_capacity: int
+    physical_replica_count: int = 1
 
     def __post_init__(self):
-        if min(self.maximum_requests, self.maximum_context_tokens, self.owners, self.page_size) < 1:
-            raise ValueError("Namespace bounds must be positive")
-
-    @property
-    def addressable_tokens_per_owner(self) -> int:
-        id_limit = (2 ** 31 - 1) // self.owners
-        need = self.maximum_requests * self.maximum_context_tokens // self.owners
-        return min(id_limit, need) // self.page_size * self.page_size
+        if min(self.device_record_capacity, self.host_record_capacity) < 0 or self.physical_replica_count < 1:
+            raise ValueError("Capacities are non-negative and an owner exists at least once")
 
 
-def calculate_addressable_history_capacity(bounds: RequestNamespaceCapacityBounds, planned_tokens_per_owner: int) -> int:
-    """Tokens per owner worth provisioning: never more than the namespace can address."""
-    return min(planned_tokens_per_owner, bounds.addressable_tokens_per_owner)
+@dataclass(frozen=True)
+class RequiredCachePartitionCapacity:
+    """One storage partition that every token of a request namespace needs (the KV tier, a compressed tier, an
+    Index tier ...).  The record counts cover all payload banks of the partition: layers and storage aliases do not
+    multiply history capacity."""
+
+    request_namespace_id: int
+    partition_name: str
+    storage_layout: object                       # StorageLayout (name, tokens_per_record)
+    record_owners: tuple
+    reserved_logical_record_count: int = 0
+
+
+@dataclass(frozen=True)
+class RequestNamespaceCapacityBounds:
+    """Token limits of one independent allocation domain that are not storage: what its allocator can hand out,
+    and what its request addressing (page tables, int32 ids) can name.  Ranks that share one allocator are ONE
+    namespace."""
+
+    request_namespace_id: int
+    native_allocator_usable_token_slots: int
+    request_address_token_slots: int
+
+    def __post_init__(self):
+        if min(self.native_allocator_usable_token_slots, self.request_address_token_slots) < 0:
+            raise ValueError("Allocator and address limits are non-negative")
+
+
+def _partition_account(part: RequiredCachePartitionCapacity) -> dict:
+    owners = tuple(part.record_owners)
+    if len({o.owner_rank for o in owners}) != len(owners):
+        raise ValueError("An owner appears once per partition")
+    device = sum(o.device_record_capacity for o in owners)
+    host = sum(o.host_record_capacity for o in owners)
+    if not 0 <= part.reserved_logical_record_count <= device + host:
+        raise ValueError("The reserved records must fit inside the partition")
+    per_record = getattr(part.storage_layout, "tokens_per_record", 1)
+    return dict(
+        request_namespace_id=part.request_namespace_id, partition_name=part.partition_name,
+        storage_layout_name=getattr(part.storage_layout, "name", str(part.storage_layout)),
+        tokens_per_record=per_record, record_owner_count=len(owners),
+        record_owners=[dict(owner_rank=o.owner_rank, device_record_capacity=o.device_record_capacity,
+                            host_record_capacity=o.host_record_capacity,
+                            physical_replica_count=o.physical_replica_count) for o in owners],
+        unique_device_cold_record_slots=device, unique_host_cold_record_slots=host,
+        physical_device_cold_record_slots=sum(o.device_record_capacity * o.physical_replica_count for o in owners),
+        physical_host_cold_record_slots=sum(o.host_record_capacity * o.physical_replica_count for o in owners),
+        reserved_logical_record_count=part.reserved_logical_record_count,
+        usable_history_token_slots=(device + host - part.reserved_logical_record_count) * per_record)
+
+
+def calculate_addressable_history_capacity(required_partitions, namespace_bounds) -> dict:
+    """History tokens a deployment can hold, as an audit: per partition the disjoint owners are summed (replicas
+    are not); a namespace holds what its SMALLEST required partition holds, capped by its allocator and by its
+    addressing; namespaces add up.  This is accounting of allocations: it says nothing about the working set,
+    running concurrency or memory peaks."""
+    parts = [_partition_account(p) for p in required_partitions]
+    bounds = tuple(namespace_bounds)
+    ids = {b.request_namespace_id for b in bounds}
+    if len(ids) != len(bounds):
+        raise ValueError("One bound per request namespace")
+    if {p["request_namespace_id"] for p in parts} != ids:
+        raise ValueError("Every namespace needs both its partitions and its bounds")
+    namespaces = []
+    for b in bounds:
+        mine = [p for p in parts if p["request_namespace_id"] == b.request_namespace_id]
+        cold = min(p["usable_history_token_slots"] for p in mine)
+        namespaces.append(dict(
+            request_namespace_id=b.request_namespace_id, required_partition_names=[p["partition_name"] for p in mine],
+            cold_storage_history_token_slots=cold,
+            native_allocator_usable_token_slots=b.native_allocator_usable_token_slots,
+            request_address_token_slots=b.request_address_token_slots,
+            usable_history_token_slots=min(cold, b.native_allocator_usable_token_slots, b.request_address_token_slots)))
+    return dict(required_partitions=parts, request_namespaces=namespaces,
+                total_usable_history_token_slots=sum(n["usable_history_token_slots"] for n in namespaces))
 
 
 def position_residency_bytes(*, tokens: int, record_bytes: int, layers: int, degree: int) -> int:

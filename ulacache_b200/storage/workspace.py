@@ -102,3 +102,46 @@ def colour_workspaces(lifetimes: Sequence[AttentionWorkspaceLifetime]) -> Tuple[
             colours[i] = len(free_at)
             free_at.append(lt.last_layer)
     return colours, len(free_at)
+
+
+CacheLayout = PoolLayout                     # the name the reference exports for a pool's byte layout
+
+
+@dataclass(frozen=True)
+class ResidentQueryLayout(PoolLayout):
+    """A pool whose big buffers are sized from the number of REAL queries that can be resident, not from the
+    power-of-two bound that per-query metadata is padded to.  ``max_queries`` stays that padded bound (a power of
+    two, at most 2048); ``max_resident_queries`` (0 = the padded bound) is what the pulled-record cache and the
+    selections are sized for.
+
+    Reference: ulacache/storage/workspace.py:263-305."""
+
+    max_resident_queries: int = 0
+
+    def __post_init__(self):
+        super().__post_init__()
+        q = self.max_queries
+        if not 0 < q <= 2048 or q & (q - 1):
+            raise ValueError("Per-query metadata is padded to a power of two of at most 2048")
+        if not 0 <= self.max_resident_queries <= q:
+            raise ValueError("Resident queries cannot exceed the metadata bound")
+
+    @property
+    def resident_query_capacity(self) -> int:
+        return self.max_resident_queries or self.max_queries
+
+    @property
+    def cache_rows(self) -> int:
+        if not self.pulled_record_cache:
+            return 0
+        return request_history_capacity(self.resident_query_capacity, self.topk, self.cache_multiplier)
+
+    @property
+    def selected_bytes(self) -> int:
+        return self.groups * self.resident_query_capacity * self.topk * 4 * 2
+
+    @property
+    def rows_per_layer(self) -> int:
+        """Pulled-record rows plus one current record per resident query, whole pages."""
+        rows = self.cache_rows + self.resident_query_capacity
+        return (rows + PAGE_TOKENS - 1) // PAGE_TOKENS * PAGE_TOKENS
