@@ -121,3 +121,99 @@ def test_resident_query_layout_sizes_from_real_queries():
     for bad in (dict(max_queries=100), dict(max_queries=4096), dict(max_queries=64, max_resident_queries=65)):
         with pytest.raises(ValueError):
             ResidentQueryLayout(**{**base, **bad})
+
+
+def _client(backend=None, **kw):
+    import dataclasses
+
+    import ulacache_b200 as ula
+    from ulacache_b200.bindings import LocalCacheBindings
+
+    from helpers import make_spec
+
+    b = LocalCacheBindings(device="cpu")
+    if backend:
+        b = dataclasses.replace(b, execution_options=dataclasses.replace(b.execution_options, record_storage_backend=backend))
+    return ula.init(make_spec(**kw), b)
+
+
+def test_client_forwards_engine_capabilities_of_the_native_paged_backend():
+    import torch
+
+    from ulacache_b200.ops import records
+
+    from helpers import random_kv
+
+    cache = _client("native_paged", layers=2, device_pages=4, host_pages=16, queries=8, topk=64)
+    assert cache.supports_local_native_current_publication is False      # true on a GPU only
+    ids = cache.alloc(320)
+    latent, rope = random_kv(320, 4)
+    enc = records.encode_scaled656(latent, rope)
+    # native segments (latent + scales | rope) concatenate to records; a wrong width is refused
+    cache.write_native_record_segments(0, ids, (enc[:, :528], enc[:, 528:]))
+    with pytest.raises(ValueError):
+        cache.write_native_record_segments(0, ids, (enc[:, :528],))
+    assert torch.equal(cache.engine.read_records(0, ids)[0], enc)
+    # native pages + source rows
+    pages = enc.flip(0).contiguous().view(5, 64, 656)
+    cache.write_native_paged_records(1, ids[:100], pages, torch.arange(319, 219, -1))
+    assert torch.equal(cache.engine.read_records(1, ids[:100])[0], enc[:100])
+    # prefill: eager union, then a borrowed chunk
+    sel = ids[torch.randperm(320, generator=torch.Generator().manual_seed(0))[:128]].view(2, 64)
+    cache.begin_model_forward()
+    view = cache.prepare_prefill_attention_inputs(0, sel)
+    assert view.records_per_page == 64 and view.device_record_indices.shape == sel.shape
+    assert torch.equal(view.gpu_buffer[view.device_record_indices[0].long()], enc[(sel[0] - ids[0]).long()])
+    cache.finish_layer_attention(0)
+    cache.finish_model_forward()
+    chunk = cache.prepare_prefill_record_chunk(1, ids[:64])
+    assert bool((chunk.device_record_indices >= 0).all())
+    with pytest.raises(RuntimeError):
+        cache.prepare_prefill_record_chunk(1, ids[64:128])            # the domain's chunk is still borrowed
+    cache.finish_prefill_record_chunk(1)
+    # hints that this engine does not implement are harmless; receive rows and inventories are forwarded
+    assert cache.prepare_forward_current_records(ids[:4]) is False
+    cache.prepare_next_residency_epochs()
+    cache.prepare_layer_execution(0)
+    fresh = torch.arange(1024, 1088, dtype=torch.int32)              # ids the framework's own allocator handed out
+    rows = cache.register_receive_records(fresh)
+    assert rows.numel() == 64 and bool((rows >= 0).all()) and rows.unique().numel() == 64
+    cache.release_logical_records(fresh)
+    assert cache.get_device_storage_inventory() and cache.get_host_storage_inventory()
+    assert cache.get_memory_inventory() == cache.memory_inventory()
+    assert len(cache.get_device_record_planes(0)) == 1 and cache.device_record_storage.shape[0] == 2
+    with pytest.raises(NotImplementedError):
+        cache.prepare_native_prefill_read_plan(sel)                   # no windowed reader bound
+    cache.close()
+
+
+def test_client_refuses_capabilities_the_backend_lacks_and_serves_a_bound_reader():
+    import torch
+
+    cache = _client(None, layers=1, device_pages=4, host_pages=4)
+    assert not cache.supports_local_native_current_publication
+    ids = cache.alloc(64)
+    for call in (lambda: cache.register_receive_records(ids), lambda: cache.prepare_prefill_record_chunk(0, ids),
+                 lambda: cache.write_native_paged_records(0, ids, torch.zeros(64, 656, dtype=torch.uint8), torch.arange(64))):
+        with pytest.raises(NotImplementedError):
+            call()
+    with pytest.raises(ValueError):
+        cache.write_native_paged_records(0, ids, None, None, local_device_after_commit=True)
+    inv = cache.get_device_storage_inventory()
+    assert sum(inv.values()) >= 4 * 64 * 656 and sum(cache.get_host_storage_inventory().values()) >= 4 * 64 * 656
+
+    class Reader:
+        def prepare_read_plan(self, ids):
+            return ("plan", int(ids.numel()))
+
+        def read_records(self, layer, ids, consume, *, output_buffer=None, read_plan=None):
+            return (layer, read_plan, output_buffer)
+
+        def attend(self, layer, query, selection, lengths, fn):
+            return fn(query)
+
+    cache.bind_prefill_reader(Reader())
+    assert cache.prepare_native_prefill_read_plan(ids) == ("plan", 64)
+    assert cache.read_native_prefill_records(0, ids, None, output="buf", read_plan="p") == (0, "p", "buf")
+    assert cache.attend_native_prefill_records(0, 3, ids, None, lambda q: q + 1) == 4
+    cache.close()

@@ -137,6 +137,114 @@ class UnifiedMemoryCache:
         post-write barrier of the peer-to-peer transport is skipped."""
         self._live().remote_readers = False
 
+    # ------------------------------------------- optional engine capabilities --
+    # A serving adapter calls these on every backend; an engine that has the capability runs it, one that does
+    # not either ignores the hint (the ``prepare_*`` calls that only move work earlier) or refuses clearly.
+    def _capability(self, name: str, why: str):
+        fn = getattr(self._live(), name, None)
+        if fn is None:
+            raise NotImplementedError(f"{type(self._engine).__name__} has no {name}: {why}")
+        return fn
+
+    def register_receive_records(self, ids):
+        """Give incoming records canonical destinations before their addresses are published to a sender."""
+        return self._capability("allocate_receive_rows", "receives go through the staging window on this backend")(ids)
+
+    def prepare_forward_current_records(self, current_ids) -> bool:
+        """Hint: all layers of this forward write the same current records.  True when the engine bound them once."""
+        fn = getattr(self._live(), "prepare_forward_current_records", None)
+        return bool(fn(current_ids)) if fn is not None else False
+
+    def prepare_next_residency_epochs(self):
+        """Hint: retire expiring recency buckets before the forward instead of inside each layer's transaction."""
+        fn = getattr(self._live(), "prepare_next_residency_epochs", None)
+        if fn is not None:
+            fn()
+
+    def prepare_layer_execution(self, layer: int):
+        """Wait for whatever was prefetched for ``layer`` (a no-op without a prefetcher)."""
+        fn = getattr(self._live(), "before_layer_prepare", None)
+        if fn is not None:
+            fn(layer)
+
+    def write_native_record_segments(self, layer: int, ids, record_segments):
+        """Publish records given as their native byte segments (plane order, then segment order, scales
+        included): uint8 tensors ``[n, segment bytes]`` that concatenate to whole records."""
+        import torch
+
+        parts = [seg.reshape(seg.shape[0], -1).view(torch.uint8) for seg in record_segments]
+        want = self.cache_specification.storage_layout.bytes_per_token
+        if sum(p.shape[1] for p in parts) != want:
+            raise ValueError(f"the segments add up to {sum(p.shape[1] for p in parts)} bytes per record, not {want}")
+        return self.write(ids, layer, parts[0] if len(parts) == 1 else torch.cat(parts, dim=1))
+
+    @property
+    def supports_local_native_current_publication(self) -> bool:
+        return bool(getattr(self._live(), "supports_local_native_current_publication", False))
+
+    def write_native_paged_records(self, layer: int, ids, source_record_pages, source_record_indices, *,
+                                   local_device_after_commit: bool = False):
+        """Publish records that sit encoded in native pages; see ``NativePagedResidency.write_native_paged_records``."""
+        if local_device_after_commit and not self.supports_local_native_current_publication:
+            raise ValueError("local current publication needs native paged storage on a GPU")
+        fn = self._capability("write_native_paged_records", "bind record_storage_backend='native_paged'")
+        if local_device_after_commit:
+            return fn(layer, ids, source_record_pages, source_record_indices, local_device_after_commit=True)
+        return fn(layer, ids, source_record_pages, source_record_indices)
+
+    def _inputs_for_rows(self, layer: int, device_rows) -> ResidentAttentionInputs:
+        from dataclasses import replace
+
+        engine = self._live()
+        planes = (engine.get_device_record_planes(layer) if hasattr(engine, "get_device_record_planes")
+                  else tuple(engine.layer_plane(layer, p) for p in range(len(engine.planes))))
+        template = ResidentAttentionInputs(record_planes=tuple(planes), device_record_indices=device_rows,
+                                           records_per_page=self.cache_specification.storage_layout.records_per_page)
+        return replace(template, pool_view=planes[0] if len(planes) == 1 else None)
+
+    def prepare_prefill_attention_inputs(self, layer: int, selected_ids) -> ResidentAttentionInputs:
+        """Eager prefill: the union of the selection becomes resident, the selection comes back as device rows."""
+        rows = self._capability("plan_prefill", "prefill on this backend goes through the prefill windows")(layer, selected_ids)
+        return self._inputs_for_rows(layer, rows)
+
+    def prepare_prefill_record_chunk(self, layer: int, ids) -> ResidentAttentionInputs:
+        """Borrow one bounded chunk of records (for reconstruction into the caller's workspace)."""
+        rows = self._capability("prepare_prefill_record_chunk", "no borrowed-chunk interface")(layer, ids)
+        return self._inputs_for_rows(layer, rows)
+
+    def finish_prefill_record_chunk(self, layer: int):
+        self._capability("finish_prefill_record_chunk", "no borrowed-chunk interface")(layer)
+
+    def bind_prefill_reader(self, reader):
+        """Attach the windowed prefill reader (``cache.prefill.window.WindowedPrefillReader``) that serves the three
+        ``*_native_prefill_*`` calls of a tensor-parallel pool."""
+        self._prefill_reader = reader
+
+    def _reader(self):
+        reader = getattr(self, "_prefill_reader", None)
+        if reader is None:
+            raise NotImplementedError("no windowed prefill reader is bound: this backend uses its resident chunk interface")
+        return reader
+
+    def prepare_native_prefill_read_plan(self, selected_ids):
+        """Window plan of a prefill selection (no KV is read)."""
+        return self._reader().prepare_read_plan(selected_ids)
+
+    def read_native_prefill_records(self, layer: int, selected_ids, native_reader, *, output, read_plan=None):
+        """Run the caller's reader over the bounded windows of the selection; it gets borrowed pages and remapped ids."""
+        return self._reader().read_records(layer, selected_ids, native_reader, output_buffer=output, read_plan=read_plan)
+
+    def attend_native_prefill_records(self, layer: int, query, selected_ids, lengths, native_attention):
+        """Hand whole query windows to the caller's attention; selection and causal length stay paired per query."""
+        return self._reader().attend(layer, query, selected_ids, lengths, native_attention)
+
+    def offload_prefill_records(self, residency_group: int, ids):
+        """Move a finished prefill's records of one residency group to the host tier."""
+        import inspect
+
+        fn = self._capability("offload_prefill", "this backend keeps prefill records where they were written")
+        return fn(residency_group, ids) if len(inspect.signature(fn).parameters) >= 2 else fn(ids)
+
     def finish_layer_attention(self, layer: int):
         self._access.finish_layer(layer)
 
@@ -156,6 +264,47 @@ class UnifiedMemoryCache:
 
     def storage_inventory(self) -> dict:
         return self._live().storage_inventory()
+
+    def get_memory_inventory(self) -> dict:
+        return self.memory_inventory()
+
+    def get_device_storage_inventory(self) -> dict:
+        """Backing device allocations by address -> bytes, each counted once."""
+        engine = self._live()
+        if hasattr(engine, "device_storage_inventory"):
+            return engine.device_storage_inventory()
+        out = {}
+        for st in engine.storages:
+            storage = st.gpu.untyped_storage()
+            out[storage.data_ptr()] = storage.nbytes()
+        return out
+
+    def get_host_storage_inventory(self) -> dict:
+        """Pinned host allocations by address -> bytes, each counted once."""
+        engine = self._live()
+        if hasattr(engine, "host_storage_inventory"):
+            return engine.host_storage_inventory()
+        out = {}
+        for st in engine.storages:
+            if st.host is not None:
+                storage = st.host.untyped_storage()
+                out[storage.data_ptr()] = storage.nbytes()
+        return out
+
+    def get_device_record_planes(self, layer: int):
+        """Every device plane of ``layer`` (borrowed; geometry is in the specification)."""
+        engine = self._live()
+        if hasattr(engine, "get_device_record_planes"):
+            return engine.get_device_record_planes(layer)
+        return tuple(engine.layer_plane(layer, p) for p in range(len(engine.planes)))
+
+    @property
+    def device_record_storage(self):
+        """The single device plane ``[layers, slots, record_bytes]``; several planes: ``get_device_record_planes``."""
+        engine = self._live()
+        if len(engine.planes) != 1:
+            raise ValueError("several planes are bound; use get_device_record_planes")
+        return engine.gpu
 
     def counters(self) -> dict:
         return self._live().counters()
