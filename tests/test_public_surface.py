@@ -217,3 +217,26 @@ def test_client_refuses_capabilities_the_backend_lacks_and_serves_a_bound_reader
     assert cache.read_native_prefill_records(0, ids, None, output="buf", read_plan="p") == (0, "p", "buf")
     assert cache.attend_native_prefill_records(0, 3, ids, None, lambda q: q + 1) == 4
     cache.close()
+
+
+def test_factory_refuses_policies_that_cannot_do_what_they_say():
+    import dataclasses
+
+    import ulacache_b200 as ula
+    from ulacache_b200.bindings import LocalCacheBindings, PositionShardBindings
+    from ulacache_b200.storage.layout import PositionShardLayout
+
+    from helpers import make_spec
+
+    b = LocalCacheBindings(device="cpu")
+    ahead = dataclasses.replace(b, execution_options=dataclasses.replace(b.execution_options,
+                                                                        copy_follower_records_asynchronously=True))
+    with pytest.raises(ValueError):
+        ula.init(make_spec(layers=4), ahead)                           # no shared selection group: nothing to copy ahead
+    cache = ula.init(make_spec(layers=4, shared_groups=((0, 1), (2, 3))), ahead)
+    cache.close()
+    with pytest.raises(ValueError):
+        ula.init(make_spec(), PositionShardBindings(device="cpu", position_layout=PositionShardLayout(1), rank=0))
+    with pytest.raises(ValueError):                                    # 16 queries x 64 records per rank > 2 pages
+        ula.init(make_spec(device_pages=2, queries=16, topk=128),
+                 PositionShardBindings(device="cpu", position_layout=PositionShardLayout(2), rank=0))
