@@ -56,6 +56,55 @@ def trace_from_file(path: str, layer: int = 0):
             yield ids, [0] * len(ids)
 
 
+def trace_from_frames(path: str, layer: int = 0):
+    """Replay input out of a framed capture (``capture_decode_frames``): per step the lookups of one layer as
+    (ids, requests), current records and padding removed, request identity kept."""
+    import numpy as np
+    import torch
+    from ..telemetry.sparse_trace import frames_to_lookups
+
+    z = np.load(path)
+    chunk = dict(frame_count=int(z["selected"].shape[0]), selected=torch.from_numpy(z["selected"]),
+                 current=torch.from_numpy(z["current"]), seen=torch.from_numpy(z["seen"]))
+    yield from frames_to_lookups(chunk, z["query_requests"].tolist(), group=layer)
+
+
+def capture_decode_frames(path: str, *, steps: int, batch: int, prompt_len: int, layers: int, tiny: bool):
+    """Like ``capture_decode_trace`` but framed: every step stores, per layer, each row's selection AND the record
+    the row is writing, plus the allocation events, in one ``.npz`` (selected [steps, layers, batch, topk],
+    current [steps, layers, batch], seen, epochs, events, query_requests).  Returns the receipt."""
+    import numpy as np
+    import torch
+    from ..models.dsa_moe import DsaMoeConfig
+    from ..serving.engine import DecodeEngine
+    from ..telemetry.sparse_trace import FramedSparseTrace, SparseTraceGeometry
+
+    cfg = DsaMoeConfig().tiny(layers=layers, topk=128) if tiny else DsaMoeConfig(layers=layers, unique_layer_weights=min(layers, 4))
+    eng = DecodeEngine(cfg, batch=batch, prompt_len=prompt_len, max_new_tokens=steps + 8, mode="dpa", use_graph=False)
+    eng.fill_synthetic()
+    geo = SparseTraceGeometry(groups=cfg.layers, query_rows=batch, topk=cfg.topk, frames=steps, chunk_frames=steps,
+                              event_capacity=max(64, 2 * steps * batch))
+    rec = FramedSparseTrace(geo, device=eng.device)
+    rec.start()
+    for step in range(steps):
+        eng.model.record_selections, eng.model.record_current = [], []
+        rec.begin_frame(batch)
+        eng.step_device()
+        for lay, (sel, cur) in enumerate(zip(eng.model.record_selections, eng.model.record_current)):
+            rec.observe(lay, sel, cur.reshape(-1)[:batch], step)
+        rec.observe_event(eng.model.record_current[0], release=False)
+    eng.model.record_selections = eng.model.record_current = None
+    eng.check()
+    chunk = rec.drain_chunk()
+    events = rec.event_snapshot()
+    rec.stop()
+    eng.close()
+    np.savez(path, selected=chunk["selected"].numpy(), current=chunk["current"].numpy(), seen=chunk["seen"].numpy(),
+             epochs=chunk["epochs"].numpy(), events=events.numpy(), query_requests=np.arange(batch, dtype=np.int64))
+    saved = path if path.endswith(".npz") else path + ".npz"
+    return dict(path=saved, sha256=_sha256(saved), steps=steps, layers=cfg.layers, batch=batch, events=int(events.shape[0]))
+
+
 def capture_decode_trace(path: str, *, steps: int, batch: int, prompt_len: int, layers: int, tiny: bool, layer: int = 0):
     """Run ``steps`` eager decode steps of an engine filled with synthetic history, append every layer's
     selection to the device trace ring, drain it between steps and save the trace.  Returns the triples saved."""
@@ -194,6 +243,11 @@ def run(steps_iter, capacity: int, per_request: int, record_bytes: int, layers: 
     return rows
 
 
+def _load(path: str):
+    """A saved trace by its form: ``.npz`` = framed capture, ``.npy`` = (step, layer, id) triples."""
+    return trace_from_frames(path) if path.endswith(".npz") else trace_from_file(path)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--trace", default="")
@@ -209,6 +263,8 @@ def main():
     ap.add_argument("--capture-batch", type=int, default=4)
     ap.add_argument("--capture-prompt", type=int, default=4096)
     ap.add_argument("--capture-layers", type=int, default=4)
+    ap.add_argument("--framed", action="store_true",
+                    help="with --capture: framed capture (.npz: selections, current records, events, request of every row)")
     ap.add_argument("--full-width", action="store_true", help="capture from the full-width model instead of the tiny one")
     ap.add_argument("--gpu-timing", action="store_true", help="also replay through the device policies with per-step timing")
     ap.add_argument("--validate", default="", help="check a captured trace and print its receipt")
@@ -223,7 +279,12 @@ def main():
         rec = compose_rank_traces(args.compose.split(","), args.compose_to, id_space_per_rank=args.id_space_per_rank)
         print(json.dumps({"experiment": "scheduler_study_compose", **rec}))
         args.trace = rec["path"]
-    if args.capture:
+    if args.capture and args.framed:
+        rec = capture_decode_frames(args.capture_to, steps=args.capture, batch=args.capture_batch,
+                                    prompt_len=args.capture_prompt, layers=args.capture_layers, tiny=not args.full_width)
+        print(json.dumps({"experiment": "scheduler_study_frames", **rec}))
+        args.trace = rec["path"]
+    elif args.capture:
         n = capture_decode_trace(args.capture_to, steps=args.capture, batch=args.capture_batch, prompt_len=args.capture_prompt,
                                  layers=args.capture_layers, tiny=not args.full_width)
         print(json.dumps({"experiment": "scheduler_study", "captured_triples": n, "trace": args.capture_to,
@@ -231,13 +292,13 @@ def main():
         args.trace = args.capture_to
     for cap in (int(c) for c in args.capacity.split(",")):
         if args.gpu_timing:
-            steps = [ids for ids, _ in (trace_from_file(args.trace) if args.trace else
+            steps = [ids for ids, _ in (_load(args.trace) if args.trace else
                                         synthetic_trace(requests=args.requests, steps=args.steps, context=args.context, topk=args.topk))]
             id_space = max(max(s) for s in steps if s) + 1
             for row in gpu_policy_timing(steps, cap, id_space):
                 print(json.dumps({"experiment": "scheduler_study_gpu", **row}))
         if args.trace:
-            steps = list(trace_from_file(args.trace))
+            steps = list(_load(args.trace))
         else:
             steps = list(synthetic_trace(requests=args.requests, steps=args.steps, context=args.context, topk=args.topk))
         for row in run(steps, cap, per_request=max(1, cap // max(1, args.requests)), record_bytes=656, layers=args.layers):

@@ -417,6 +417,7 @@ class DsaMoeModel:
         self._nvtx = _os.environ.get("ULC_NVTX", "0") == "1"
         self._nvtx_open = False
         self.record_selections = None       # a list here makes every layer append its selected record IDs
+        self.record_current = None          # ... and the ids of the records the step is writing (one per row)
         self.record_sublayers = None        # ... and (attention output, feed-forward output) of every layer
         self.record_routing = None          # ... and (expert choice, gate) of every MoE layer
         self.force_routing = None           # a list of (choice, gate) here replaces the router's decision, one
@@ -617,6 +618,8 @@ class DsaMoeModel:
             sel = torch.sort(sel, dim=1, descending=True).values.contiguous()
         if self.record_selections is not None:
             self.record_selections.append(sel.clone())          # (eager runs only: for oracles and traces)
+        if self.record_current is not None:
+            self.record_current.append(new_ids.clone())
 
         # ---- cache: residency + resolve, publish the new KV, attend
         self._mark("cache.plan+write")
