@@ -73,3 +73,60 @@ def test_byte_banks_validate_their_bindings():
         banks.write("mla_000", torch.arange(3), bytes(656 * 2))
     lay = banks.layout("f")
     assert lay.owners == 1 and lay.layers == 2 and lay.index_anchors == ()
+
+
+def test_a_striped_snapshot_restores_into_a_single_owner_cache_with_one_lookup(tmp_path):
+    import ulacache_b200 as ula
+    from ulacache_b200.bindings import LocalCacheBindings
+    from ulacache_b200.ops import records
+    from ulacache_b200.tools.snapshot import cache_io
+    from ulacache_b200.tools.snapshot.format import SnapshotLayout, finalize_snapshot
+    from ulacache_b200.tools.snapshot.restore import PreparedSequenceRestore, iter_sequence_plane, restore_request
+
+    from helpers import make_spec, random_kv
+
+    spec = make_spec(layers=2, device_pages=2, host_pages=8)
+    cache = ula.init(spec, LocalCacheBindings(device="cpu"))
+    ids = cache.alloc(320)
+    lat, rope = random_kv(320, 9)
+    for l in range(2):
+        cache.write(ids, l, (lat + l, rope))
+    layout = SnapshotLayout("m", owners=4, layers=2, mla_row_bytes=656)
+    request = SnapshotRequest("a", tuple(range(250)), (1, 2, 3))      # 252 positions: an uneven last stripe
+    path = str(tmp_path / "bank")
+    for owner in range(4):
+        cache_io.save_shard(cache, path, layout, [request], {"a": ids[:253]}, owner)
+    finalize_snapshot(path)
+    reader = SnapshotReader(path, verify_payload=True)
+    seq = torch.cat([d for _, d in iter_sequence_plane(reader, "a", "mla_001", chunk_rows=40)])
+    assert torch.equal(seq, cache.engine.read_records(1, ids[:252])[0])
+    with pytest.raises(ValueError):
+        list(iter_sequence_plane(reader, "a", "mla_001", chunk_rows=42))     # not whole stripes
+
+    fresh = ula.init(spec, LocalCacheBindings(device="cpu"))
+    new = fresh.alloc(256)[:252]
+    out = restore_request(fresh, reader, "a", new, verify=True, chunk_rows=50)
+    assert out["source_owners"] == 4 and out["restored_bytes"] == 2 * 252 * 656 and out["next_token_id"] == 3
+    for l in range(2):
+        assert torch.equal(fresh.engine.read_records(l, new)[0], cache.engine.read_records(l, ids[:252])[0])
+    # the restored records are served like any other (host-resident ones get promoted)
+    fresh.begin_model_forward()
+    fresh.access(new[200:232].view(1, 32), 1)
+    got = records.decode_scaled656(fresh.gather_selected_records(1))
+    want = records.decode_scaled656(cache.engine.read_records(1, ids[200:232])[0])
+    assert torch.equal(got, want)
+    fresh.finish_layer_attention(1)
+    fresh.finish_model_forward()
+    with pytest.raises(ValueError):
+        restore_request(fresh, reader, "a", new[:10])
+    freed = fresh.alloc(64)
+    fresh.free(freed)
+    with pytest.raises(ValueError):
+        PreparedSequenceRestore(fresh, freed)                        # no storage behind these ids
+    with PreparedSequenceRestore(fresh, new) as prepared:
+        with pytest.raises(ValueError):
+            prepared.write(0, 250, torch.zeros(8, 656, dtype=torch.uint8))
+    with pytest.raises(RuntimeError):
+        prepared.write(0, 0, torch.zeros(8, 656, dtype=torch.uint8))
+    cache.close()
+    fresh.close()
