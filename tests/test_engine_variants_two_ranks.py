@@ -177,6 +177,14 @@ def test_pulled_record_cache_policies_against_a_plain_model():
         assert cache.hits > 0 and cache.misses > 0
     small = PulledRecordCache(record_bytes=16, max_queries=1, topk=8, multiplier=3.0)
     small.begin_step()
+    rows = small.allocate([7, 9, 7])                      # a repeated id gets one row
+    assert rows[0] == rows[2] != rows[1]
+    small.fill(rows[:2], torch.arange(32, dtype=torch.uint8).view(2, 16))
+    assert small.read([rows[1]]).tolist() == [list(range(16, 32))]
+    slots, miss = small.lookup(torch.tensor([9, 8]))
+    assert slots.tolist() == [rows[1], -1] and miss.tolist() == [False, True]
+    small = PulledRecordCache(record_bytes=16, max_queries=1, topk=8, multiplier=3.0)
+    small.begin_step()
     small.allocate(list(range(small.capacity)))
     with pytest.raises(MemoryError):
         small.allocate([10_000])                          # every row is pinned by this step

@@ -65,7 +65,11 @@ class TensorParallelResidency(CacheEngine):
 class PulledRecordCache:
     """Optional per-rank cache of records pulled from peers, keyed by global ID, with
     step-age replacement (the reference's attention buffer, ulacache/cache/attention_buffers.py:30).
-    Capacity is ``max_queries * topk * multiplier`` rows (multiplier >= 3)."""
+    Capacity is ``max_queries * topk * multiplier`` rows (multiplier >= 3).
+
+    State is three tensors on ``device`` (``tags``: id held by each row or -1, ``pins``: step of last use,
+    ``storage``: the rows); lookup is a sort + binary search over the tags and victim selection a masked sort, so a
+    step costs a handful of tensor operations whatever the number of ids."""
 
     def __init__(self, *, record_bytes: int, max_queries: int, topk: int, multiplier: float = 3.0,
                  policy: str = "age_lru", device="cpu"):
@@ -77,10 +81,10 @@ class PulledRecordCache:
             raise ValueError("policy must be age_lru or circular")
         self.capacity = (int(max_queries * topk * multiplier) + 63) // 64 * 64
         self.policy = policy
+        self.device = torch.device(device)
         self.storage = torch.zeros((self.capacity, record_bytes), dtype=torch.uint8, device=device)
         self.tags = torch.full((self.capacity,), -1, dtype=torch.int64, device=device)
         self.pins = torch.zeros(self.capacity, dtype=torch.int64, device=device)
-        self.slot_of = {}
         self.step = 0
         self.hand = 0
         self.hits = self.misses = 0
@@ -88,53 +92,71 @@ class PulledRecordCache:
     def begin_step(self):
         self.step += 1
 
-    def lookup(self, ids):
-        """Return (slots, miss_mask) for a flat list of global IDs; hits are pinned."""
+    def _find(self, ids):
+        """Row of each id, -1 where the id is not cached."""
         import torch
 
-        slots = torch.full((len(ids),), -1, dtype=torch.int64)
-        for i, gid in enumerate(ids):
-            s = self.slot_of.get(int(gid))
-            if s is not None:
-                slots[i] = s
-                self.pins[s] = self.step
-                self.hits += 1
-        return slots, slots < 0
+        order = torch.argsort(self.tags)
+        ordered = self.tags[order]
+        at = torch.searchsorted(ordered, ids).clamp(max=self.capacity - 1)
+        return torch.where(ordered[at] == ids, order[at], torch.full_like(at, -1))
+
+    def lookup(self, ids):
+        """Return (slots, miss_mask) for a flat list (or tensor) of global IDs; hits are pinned."""
+        import torch
+
+        ids = torch.as_tensor(ids, dtype=torch.int64, device=self.device).reshape(-1)
+        slots = self._find(ids)
+        hit = slots >= 0
+        self.pins[slots[hit]] = self.step
+        self.hits += int(hit.sum())
+        return slots, ~hit
+
+    def _victims(self, n: int):
+        """``n`` replaceable rows: free rows first, then unpinned rows oldest first (age policy) or in ring order
+        behind the hand (circular policy).  Rows used in the current step are never taken."""
+        import torch
+
+        free = (self.tags < 0).nonzero().flatten()[:n]
+        need = n - free.numel()
+        if need == 0:
+            return free
+        usable = (self.tags >= 0) & (self.pins != self.step)
+        if int(usable.sum()) < need:
+            raise MemoryError("every cached row is pinned by the current step")
+        if self.policy == "circular":
+            ring = (torch.arange(self.capacity, device=self.device) + self.hand) % self.capacity
+            taken = ring[usable[ring]][:need]
+            self.hand = (int(taken[-1]) + 1) % self.capacity
+        else:
+            age_key = torch.where(usable, self.pins, torch.full_like(self.pins, torch.iinfo(torch.int64).max))
+            taken = torch.argsort(age_key, stable=True)[:need]
+        return torch.cat([free, taken])
 
     def allocate(self, miss_ids):
-        """Assign a slot to every missed ID, evicting the oldest unpinned rows."""
-        out = []
-        for gid in miss_ids:
-            gid = int(gid)
-            if gid in self.slot_of:
-                out.append(self.slot_of[gid])
-                continue
-            s = self._victim()
-            old = int(self.tags[s])
-            if old >= 0:
-                self.slot_of.pop(old, None)
-            self.tags[s] = gid
-            self.pins[s] = self.step
-            self.slot_of[gid] = s
-            self.misses += 1
-            out.append(s)
-        return out
-
-    def _victim(self) -> int:
+        """Assign a row to every missed ID (each distinct id once) and return the rows in the order given."""
         import torch
 
-        free = (self.tags < 0).nonzero()
-        if free.numel():
-            return int(free[0])
-        if self.policy == "circular":
-            for _ in range(self.capacity):
-                s = self.hand
-                self.hand = (self.hand + 1) % self.capacity
-                if int(self.pins[s]) != self.step:
-                    return s
-            raise MemoryError("every cached row is pinned by the current step")
-        ages = torch.where(self.pins == self.step, torch.full_like(self.pins, -1), self.step - self.pins)
-        s = int(torch.argmax(ages))
-        if int(ages[s]) < 0:
-            raise MemoryError("every cached row is pinned by the current step")
-        return s
+        ids = torch.as_tensor(miss_ids, dtype=torch.int64, device=self.device).reshape(-1)
+        if ids.numel() == 0:
+            return []
+        have = self._find(ids)
+        fresh = torch.unique(ids[have < 0])
+        if fresh.numel():
+            rows = self._victims(int(fresh.numel()))
+            self.tags[rows] = fresh
+            self.misses += int(fresh.numel())
+            have = self._find(ids)
+        self.pins[have] = self.step
+        return have.tolist()
+
+    def fill(self, rows, records):
+        """Store pulled records in their assigned rows."""
+        import torch
+
+        self.storage[torch.as_tensor(rows, dtype=torch.int64, device=self.device)] = records.to(self.device)
+
+    def read(self, rows):
+        import torch
+
+        return self.storage[torch.as_tensor(rows, dtype=torch.int64, device=self.device)]
