@@ -88,7 +88,11 @@ def test_bitmap_index_through_a_full_ring_rotation(native):
         # a few warm rows every step; two host rows every 20 steps, so most slots stay untouched long
         # enough to expire into the cold bucket and the rare victims come out of it
         warm = ids[torch.randperm(20, generator=g)[:4].cuda()]
-        extra = ids[(128 + torch.randperm(72, generator=g)[:2]).cuda()] if step % 20 == 19 else ids[:0]
+        extra = ids[:0]
+        if step % 20 == 19:
+            # which ids sit in the host tier is decided by the order registration's threads ran in: ask the directory
+            on_host = ids[gpus[1].directory[gpus[1]._owned_locals(ids)[1].long()] <= -2]
+            extra = on_host[torch.randperm(on_host.numel(), generator=g)[:2].cuda()]
         sel = torch.cat([warm, extra]).view(1, -1)
         for r in gpus:
             r.begin_step()
@@ -107,7 +111,7 @@ def test_bitmap_index_through_a_full_ring_rotation(native):
         gpus[1].check_status()
         saw_cold = max(saw_cold, int(gpus[1].ring[255]))
         gpus[0].load_state(gpus[1].state_dict())                                   # equally old victims may differ
-    assert saw_cold > 50 and gpus[1].stats()["evictions"] >= 10
+    assert saw_cold > 50 and gpus[1].stats()["evictions"] >= 10, gpus[1].stats()
     kept = gpus[1].bits.clone()
     gpus[1].rebuild_victim_index()
     assert torch.equal(kept, gpus[1].bits)
@@ -232,4 +236,37 @@ def test_file_restore_alternates_two_pinned_buffers(native, tmp_path):
     assert stats["chunks_read"] == 5 and stats["payload_sha256_verified"] and stats["leased_buffers"] == 0
     assert torch.equal(cache.engine.read_records(0, ids)[0].cpu(), payload)
     cache.check()
+    cache.close()
+
+
+def test_canary_build_of_the_storage_on_cuda(native, monkeypatch):
+    """ULC_CANARY=1: guard records around every layer's device and pinned host plane survive writes, promotions
+    and evictions through the kernels (planes become strided views), and a byte written past a plane is reported."""
+    from ulacache_b200.storage.buffers import GUARD_ROWS
+
+    monkeypatch.setenv("ULC_CANARY", "1")
+    cache = ula.init(make_spec(device_pages=4, host_pages=16), LocalCacheBindings(device="cuda"))
+    st = cache.engine.storages[0]
+    assert st.guard == GUARD_ROWS and not st.gpu.is_contiguous()
+    ids = cache.alloc(1000)
+    latent, rope = random_kv(1000, 0)
+    latent, rope = latent.cuda(), rope.cuda()
+    for layer in range(2):
+        cache.write(ids, layer, (latent * (layer + 1), rope))
+    truth = records.decode_scaled656(records.encode_scaled656(latent * 2, rope))
+    g = torch.Generator().manual_seed(1)
+    for step in range(4):
+        pick = torch.stack([torch.randperm(1000, generator=g)[:128] for _ in range(2)]).cuda()
+        cache.begin_model_forward()
+        cache.access(ids[pick], 1)
+        got = records.decode_scaled656(cache.gather_selected_records(1)).view(2, 128, 576)
+        assert (got == truth[pick]).float().mean() > 0.99
+        cache.finish_layer_attention(1)
+        cache.finish_model_forward()
+    cache.check()
+    assert cache.counters()["promotions"] > 0 and cache.counters()["evictions"] > 0
+    st._device_block[0, 0, 3] = 0
+    torch.cuda.synchronize()
+    with pytest.raises(RuntimeError, match="before the device slots"):
+        cache.check()
     cache.close()

@@ -240,3 +240,44 @@ def test_factory_refuses_policies_that_cannot_do_what_they_say():
     with pytest.raises(ValueError):                                    # 16 queries x 64 records per rank > 2 pages
         ula.init(make_spec(device_pages=2, queries=16, topk=128),
                  PositionShardBindings(device="cpu", position_layout=PositionShardLayout(2), rank=0))
+
+
+def test_canary_build_catches_a_write_outside_a_plane(monkeypatch):
+    import torch
+
+    import ulacache_b200 as ula
+    from ulacache_b200.bindings import LocalCacheBindings
+    from ulacache_b200.ops import records
+    from ulacache_b200.storage.buffers import GUARD_BYTE, GUARD_ROWS
+
+    from helpers import make_spec, random_kv
+
+    monkeypatch.setenv("ULC_CANARY", "1")
+    cache = ula.init(make_spec(layers=2, device_pages=2, host_pages=4), LocalCacheBindings(device="cpu"))
+    st = cache.engine.storages[0]
+    assert st.guard == GUARD_ROWS and st.gpu.shape[1] == 128 and st.host.shape[1] == 256
+    assert st.device_bytes() == 2 * (128 + 2 * GUARD_ROWS) * 656
+    ids = cache.alloc(300)                                           # fills the device tier and spills to the host
+    latent, rope = random_kv(300, 1)
+    for layer in range(2):
+        cache.write(ids, layer, (latent, rope))
+    cache.begin_model_forward()
+    cache.access(ids[200:264].view(1, 64), 1)                        # promotions and evictions through both tiers
+    got = records.decode_scaled656(cache.gather_selected_records(1))
+    assert torch.equal(got, records.decode_scaled656(records.encode_scaled656(latent, rope))[200:264])
+    cache.finish_layer_attention(1)
+    cache.finish_model_forward()
+    cache.check()                                                    # every guard record is intact
+    st._device_block[1, GUARD_ROWS + 128, 5] = 0                     # one byte past layer 1's last device slot
+    with pytest.raises(RuntimeError, match="after the device slots of storage layer"):
+        cache.check()
+    st._device_block[1, GUARD_ROWS + 128, 5] = GUARD_BYTE
+    st.host_pool.storage[0, GUARD_ROWS - 1, 0] = 1                   # and one before layer 0's first host slot
+    with pytest.raises(RuntimeError, match="before the host slots"):
+        cache.check()
+    cache.close()
+    monkeypatch.setenv("ULC_CANARY", "0")
+    plain = ula.init(make_spec(layers=1), LocalCacheBindings(device="cpu"))
+    assert plain.engine.storages[0].guard == 0 and plain.engine.storages[0].gpu.is_contiguous()
+    plain.check()
+    plain.close()

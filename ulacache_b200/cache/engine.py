@@ -518,7 +518,12 @@ class CacheEngine:
         return out
 
     def check(self, what="cache step"):
-        """Read back device status words (synchronises); raises on any kernel-reported error."""
+        """Read back device status words (synchronises); raises on any kernel-reported error, and, in the
+        canary build of the storage, on an overwritten guard record."""
+        for st in self.storages:
+            check = getattr(st, "check_canaries", None)
+            if check is not None:
+                check()
         if not self.is_cuda:
             return
         from ..ops import _native as N

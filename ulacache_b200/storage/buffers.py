@@ -84,6 +84,20 @@ def default_host_pool_factory(*, layers, slots, row_bytes, device=None):
     return PinnedHostRecordPool(layers=layers, slots=slots, row_bytes=row_bytes, device=device)
 
 
+GUARD_ROWS = 4
+GUARD_BYTE = 0xA5
+
+
+def canaries_enabled(environ=None) -> bool:
+    """``ULC_CANARY=1``: a debug build of the record storage.  Every layer's device plane and host plane gets
+    ``GUARD_ROWS`` guard records before its first slot and after its last, filled with ``GUARD_BYTE``; ``check``
+    on the cache verifies them, so a kernel that writes outside its plane is caught at the next check instead of
+    corrupting a neighbouring layer's records."""
+    import os
+
+    return (environ if environ is not None else os.environ).get("ULC_CANARY", "0") == "1"
+
+
 @dataclass
 class PlaneGeometry:
     layers: int
@@ -102,22 +116,50 @@ class RecordPlaneStorage:
         self.plane = plane
         self.geometry = PlaneGeometry(layers, hbm_slots, host_slots, plane.bytes_per_record)
         self.device = torch.device(device)
-        self.gpu = torch.zeros((layers, hbm_slots, plane.bytes_per_record), dtype=torch.uint8, device=self.device)
+        self.guard = GUARD_ROWS if canaries_enabled() else 0
+        g = self.guard
+        self._device_block = torch.zeros((layers, hbm_slots + 2 * g, plane.bytes_per_record), dtype=torch.uint8,
+                                         device=self.device)
+        self.gpu = self._device_block[:, g:g + hbm_slots] if g else self._device_block
         self.host_pool = None
         if host_slots > 0:
             if self.device.type == "cuda":
-                self.host_pool = host_pool_factory(layers=layers, slots=host_slots,
+                self.host_pool = host_pool_factory(layers=layers, slots=host_slots + 2 * g,
                                                    row_bytes=plane.bytes_per_record, device=self.device)
             else:
-                self.host_pool = PinnedHostRecordPool(layers=layers, slots=host_slots,
+                self.host_pool = PinnedHostRecordPool(layers=layers, slots=host_slots + 2 * g,
                                                       row_bytes=plane.bytes_per_record, pin=False)
+        if g:
+            for block in (self._device_block, None if self.host_pool is None else self.host_pool.storage):
+                if block is not None:
+                    block[:, :g] = GUARD_BYTE
+                    block[:, block.shape[1] - g:] = GUARD_BYTE
 
     @property
     def host(self):
-        return None if self.host_pool is None else self.host_pool.storage
+        if self.host_pool is None:
+            return None
+        g = self.guard
+        return self.host_pool.storage[:, g:g + self.geometry.host_slots] if g else self.host_pool.storage
+
+    def check_canaries(self):
+        """Raise when a guard record of any layer has been overwritten (no-op without ``ULC_CANARY=1``)."""
+        g = self.guard
+        if not g:
+            return
+        for tier, block in (("device", self._device_block),
+                            ("host", None if self.host_pool is None else self.host_pool.storage)):
+            if block is None:
+                continue
+            for side, rows in (("before", block[:, :g]), ("after", block[:, block.shape[1] - g:])):
+                bad = (rows != GUARD_BYTE).reshape(rows.shape[0], -1).any(dim=1)
+                if bool(bad.any()):
+                    layers = bad.nonzero().flatten().tolist()
+                    raise RuntimeError(f"plane {self.plane.name!r}: guard records {side} the {tier} slots of storage "
+                                       f"layer(s) {layers} were overwritten")
 
     def device_bytes(self) -> int:
-        return self.gpu.numel()
+        return self._device_block.numel()
 
     def host_bytes(self) -> int:
         return 0 if self.host_pool is None else self.host_pool.nbytes
@@ -126,4 +168,4 @@ class RecordPlaneStorage:
         if self.host_pool is not None:
             self.host_pool.close()
         self.host_pool = None
-        self.gpu = None
+        self.gpu = self._device_block = None
