@@ -281,3 +281,26 @@ def test_canary_build_catches_a_write_outside_a_plane(monkeypatch):
     assert plain.engine.storages[0].guard == 0 and plain.engine.storages[0].gpu.is_contiguous()
     plain.check()
     plain.close()
+
+
+def test_heap_carved_planes_keep_the_storage_interface():
+    """Planes that live in the symmetric heap skip the base constructor; they must still answer everything the
+    engine asks of a plane storage (host view, guard check, byte counts)."""
+    import torch
+
+    from ulacache_b200.cache.engine import _HeapPlaneStorage
+    from ulacache_b200.storage.buffers import PinnedHostRecordPool
+    from ulacache_b200.storage.layout import MLA_SCALED656
+
+    class Heap:
+        device = torch.device("cpu")
+
+        def alloc(self, name, shape, dtype):
+            return torch.zeros(shape, dtype=dtype)
+
+    st = _HeapPlaneStorage(MLA_SCALED656, heap=Heap(), layers=2, hbm_slots=64, host_slots=128,
+                           host_pool_factory=lambda **kw: PinnedHostRecordPool(pin=False, **{k: v for k, v in kw.items() if k != "device"}))
+    assert st.guard == 0 and st.host.shape == (2, 128, 656) and st.device_bytes() == 2 * 64 * 656
+    st.check_canaries()
+    assert st.host_bytes() == 2 * 128 * 656
+    st.close()

@@ -574,6 +574,7 @@ class _HeapPlaneStorage(RecordPlaneStorage):
         self.geometry = PlaneGeometry(layers, hbm_slots, host_slots, plane.bytes_per_record)
         self.device = heap.device
         self.gpu = heap.alloc(f"plane.{plane.name}.{id(self)}", (layers, hbm_slots, plane.bytes_per_record), torch.uint8)
+        self.guard, self._device_block = 0, self.gpu      # peers address these planes: no guard records in the heap
         self.host_pool = None
         if host_slots > 0:
             self.host_pool = host_pool_factory(layers=layers, slots=host_slots, row_bytes=plane.bytes_per_record,
