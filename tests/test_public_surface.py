@@ -304,3 +304,28 @@ def test_heap_carved_planes_keep_the_storage_interface():
     st.check_canaries()
     assert st.host_bytes() == 2 * 128 * 656
     st.close()
+
+
+def test_launch_environment_is_derived_once_and_conflicts_are_refused():
+    import os
+
+    from ulacache_b200.config.model_configuration import (ConfigurationError, launch_environment,
+                                                          load_model_configuration)
+
+    root = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "ulacache_b200", "config", "models")
+    dpa = load_model_configuration(os.path.join(root, "b200-native-dpa.json"), environ={})
+    env = launch_environment(dpa, environ={})
+    assert int(env["UDCACHE_DPA_GPU_SLOTS"]) > 0 and int(env["UDCACHE_DPA_GPU_SLOTS"]) % 64 == 0
+    assert "UDCACHE_DPA_CPU_SLOTS" in env and all(isinstance(v, str) for v in env.values())
+    assert launch_environment(dpa, environ=dict(env)) == env                       # the same values are no conflict
+    with pytest.raises(ConfigurationError, match="conflicts"):
+        launch_environment(dpa, environ={"UDCACHE_DPA_GPU_SLOTS": "64"})
+    with pytest.raises(ConfigurationError, match="legacy"):
+        launch_environment(dpa, environ={"ULACACHE_QSA_CONFIGURATION": "x.json"})
+    with pytest.raises(ConfigurationError, match="legacy"):
+        load_model_configuration(os.path.join(root, "b200-native-dpa.json"), environ={"ULACACHE_V0522_CONFIGURATION": "y"})
+    tp = load_model_configuration(os.path.join(root, "native-tp-arena.json"), environ={})
+    assert set(launch_environment(tp, environ={})) == {"UDCACHE_PLAIN_PREFILL_WINDOW_ROWS", "ULACACHE_TP_LOW_QUERY_PULL_BLOCKS",
+                                                       "ULACACHE_REUSE_PREFILL_METADATA"}
+    dsa = load_model_configuration(os.path.join(root, "dsa-peer-topk.json"), environ={})
+    assert launch_environment(dsa, environ={}) == {}

@@ -300,11 +300,61 @@ def decode_model_configuration(text: str) -> ModelConfiguration:
     return ModelConfiguration(1, adapter, release, ngram, dev, host, parsed, raw=doc)
 
 
+# One configuration file replaced a family of per-adapter variables; a process that still exports one of them next
+# to the file would be configured twice, so it is refused.  Reference: patches/sglang.patch:8286-8291, :8548-8550.
+LEGACY_CONFIGURATION_VARIABLES = (
+    "ULACACHE_NATIVE_DSA_CONFIGURATION", "ULACACHE_NATIVE_PAGED_CONFIGURATION", "ULACACHE_GLM_FLASH_CONFIGURATION",
+    "ULACACHE_QSA_CONFIGURATION", "ULACACHE_NATIVE_OWNER_INDEX_CONFIGURATION", "ULACACHE_V0522_CONFIGURATION",
+)
+
+
+def launch_environment(configuration: ModelConfiguration, environ=None) -> dict:
+    """The launch variables that scripts and workers of a deployment read (slot counts, byte budgets, launch
+    shapes), derived from the one configuration so that every worker sees the same values.  A variable that is
+    already exported with a DIFFERENT value is a conflict, not an override.  Returns the variables to export
+    (the given environment is not changed).
+
+    Reference: patches/sglang.patch:8495-8530 (``configure_launch``), scripts/7_2_throughput/start_ulacache.sh:121-165."""
+    env = os.environ if environ is None else environ
+    legacy = [name for name in LEGACY_CONFIGURATION_VARIABLES if env.get(name)]
+    if legacy:
+        raise ConfigurationError(f"use ULACACHE_CONFIGURATION without the legacy configuration variables {legacy}")
+    o, out = configuration.options, {}
+    if configuration.adapter == "native_tp":
+        out = {"UDCACHE_PLAIN_PREFILL_WINDOW_ROWS": getattr(o, "prefill_window_rows", 0),
+               "ULACACHE_TP_LOW_QUERY_PULL_BLOCKS": getattr(o, "low_query_pull_blocks", 0),
+               "ULACACHE_REUSE_PREFILL_METADATA": int(bool(getattr(o, "reuse_prefill_metadata", False)))}
+    elif configuration.adapter == "native_dpa":
+        dev = configuration.device_token_capacity_per_owner or getattr(o, "device_record_capacity", 0)
+        host = configuration.host_token_capacity_per_owner or getattr(o, "host_record_capacity", 0)
+        out = {"UDCACHE_DPA_GPU_SLOTS": dev, "UDCACHE_DPA_CPU_SLOTS": host}
+        for name, field in (("UDCACHE_DPA_CACHE_BUDGET_BYTES", "device_cache_budget_bytes"),
+                            ("UDCACHE_CPU_CACHE_CAP_BYTES", "host_cache_budget_bytes"),
+                            ("UDCACHE_DPA_EXCHANGE_BLOCKS", "exchange_blocks"),
+                            ("UDCACHE_DPA_EXCHANGE_THREADS", "exchange_threads")):
+            value = getattr(o, field, None)
+            if value is not None:
+                out[name] = value
+        for name, field in (("UDCACHE_DPA_CPU_PREFILL", "cpu_prefill"), ("UDCACHE_DPA_PARALLEL_PREPARE", "parallel_prepare"),
+                            ("UDCACHE_DPA_PARALLEL_VICTIMS", "parallel_victims"),
+                            ("UDCACHE_DPA_ASYNC_FOLLOWERS", "asynchronous_followers")):
+            if hasattr(o, field):
+                out[name] = int(bool(getattr(o, field)))
+    out = {k: str(v) for k, v in out.items()}
+    for name, value in out.items():
+        if name in env and env[name] != value:
+            raise ConfigurationError(f"{name}={env[name]} in the environment conflicts with the configuration ({value})")
+    return out
+
+
 def load_model_configuration(path: Optional[str] = None, environ=None) -> Optional[ModelConfiguration]:
     """Read the file named by ``path`` or by ``ULACACHE_CONFIGURATION``; None when neither is set."""
     env = os.environ if environ is None else environ
     path = path or env.get("ULACACHE_CONFIGURATION")
     if not path:
         return None
+    legacy = [name for name in LEGACY_CONFIGURATION_VARIABLES if env.get(name)]
+    if legacy:
+        raise ConfigurationError(f"use ULACACHE_CONFIGURATION without the legacy configuration variables {legacy}")
     with open(path) as f:
         return decode_model_configuration(f.read())

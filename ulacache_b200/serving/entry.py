@@ -52,11 +52,12 @@ def start(config_path=None, *, layers: int, device="cuda", audit_dir: str = "", 
     """Build the cache client for this rank and (optionally) write its start-up receipt."""
     from .. import client
     from ..bindings import LocalCacheBindings
-    from ..config.model_configuration import load_model_configuration
+    from ..config.model_configuration import launch_environment, load_model_configuration
 
     cfg = load_model_configuration(config_path)
     if cfg is None:
         raise SystemExit("no configuration: pass --config or set ULACACHE_CONFIGURATION")
+    exports = launch_environment(cfg)               # refuses legacy variables and values that contradict the file
     rank = int(os.environ.get("RANK", "0"))
     spec = specification_from_configuration(cfg, layers=layers, max_queries=max_queries, topk=topk, scale=scale)
     cache = client.init(spec, LocalCacheBindings(device=device))
@@ -64,7 +65,7 @@ def start(config_path=None, *, layers: int, device="cuda", audit_dir: str = "", 
     receipt = {"rank": rank, "adapter": cfg.adapter, "layers": layers, "scale": scale,
                "device_record_capacity": inv["device_record_capacity"], "host_record_capacity": inv["host_record_capacity"],
                "device_key_value_bytes": inv["device_key_value_bytes"], "host_key_value_bytes": inv["host_key_value_bytes"],
-               "metadata_bytes": inv["metadata_bytes"]}
+               "metadata_bytes": inv["metadata_bytes"], "launch_environment": exports}
     if audit_dir:
         os.makedirs(audit_dir, exist_ok=True)
         with open(os.path.join(audit_dir, f"rank{rank}.json"), "w") as f:
@@ -81,6 +82,7 @@ def main():
     ap.add_argument("--scale", type=float, default=1.0)
     args = ap.parse_args()
     cache, receipt = start(args.config, layers=args.layers, device=args.device, audit_dir=args.audit_dir, scale=args.scale)
+    os.environ.update(receipt["launch_environment"])    # workers spawned from this process inherit the same settings
     print(json.dumps(receipt))
     cache.close()
 
