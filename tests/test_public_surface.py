@@ -329,3 +329,10 @@ def test_launch_environment_is_derived_once_and_conflicts_are_refused():
                                                        "ULACACHE_REUSE_PREFILL_METADATA"}
     dsa = load_model_configuration(os.path.join(root, "dsa-peer-topk.json"), environ={})
     assert launch_environment(dsa, environ={}) == {}
+
+
+def test_quickstart_example_runs_on_cpu():
+    from ulacache_b200.examples.quickstart import run
+
+    out = run("cpu", tokens=600, steps=2)
+    assert out["reads_exact"] == out["reads"] and out["promotions"] > 0 and out["unserved"] == 0
