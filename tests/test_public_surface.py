@@ -336,3 +336,25 @@ def test_quickstart_example_runs_on_cpu():
 
     out = run("cpu", tokens=600, steps=2)
     assert out["reads_exact"] == out["reads"] and out["promotions"] > 0 and out["unserved"] == 0
+
+
+def test_payload_replacement_pricing_and_workspace_bytes():
+    from ulacache_b200.storage.capacity import (CacheCapacityPlan, CacheMemoryBudget, CacheMemoryUsage,
+                                                price_payload_replacement, residency_workspace_bytes)
+
+    plan = CacheCapacityPlan(64 * 100, 64 * 300, 8, CacheMemoryUsage(80 << 30, 120 << 30), CacheMemoryBudget(90 << 30, 128 << 30))
+    usage = price_payload_replacement(native_device_bytes=70 << 30, native_payload_bytes=60 << 30,
+                                      replacement_device_bytes=64 << 30, replacement_host_bytes=100 << 30,
+                                      native_host_bytes=4 << 30, allocation_plan=plan)
+    assert usage == CacheMemoryUsage(74 << 30, 104 << 30)
+    with pytest.raises(ValueError, match="exceed"):
+        price_payload_replacement(native_device_bytes=70 << 30, native_payload_bytes=10 << 30,
+                                  replacement_device_bytes=64 << 30, replacement_host_bytes=0, allocation_plan=plan)
+    with pytest.raises(ValueError, match="part of"):
+        price_payload_replacement(native_device_bytes=1, native_payload_bytes=2, replacement_device_bytes=0,
+                                  replacement_host_bytes=0, allocation_plan=plan)
+    w = residency_workspace_bytes(4096, 61, 1 << 20)
+    assert w["fixed_bytes"] == 32 * 4096 + 56 * 61 and w["expiry_bytes"] == 4 * 61 * 4096
+    assert residency_workspace_bytes(4096, 2, 100)["expiry_bytes"] == 800
+    with pytest.raises(ValueError):
+        residency_workspace_bytes(0, 1, 1)

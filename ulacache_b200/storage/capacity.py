@@ -136,6 +136,40 @@ def plan_cache_capacity(*, memory_budget: CacheMemoryBudget, measure_memory_usag
                              cost(dev, total - dev), memory_budget)
 
 
+def price_payload_replacement(*, native_device_bytes: int, native_payload_bytes: int, replacement_device_bytes: int,
+                              replacement_host_bytes: int, native_host_bytes: int = 0,
+                              allocation_plan: CacheCapacityPlan) -> CacheMemoryUsage:
+    """What a deployment costs when the pooled cache REPLACES a framework's own KV payload: everything else the
+    framework charged on the device (index, request tables, sliding state, allocator headroom) stays, only the
+    payload named here is subtracted, and the pool's device and host bytes are added.  The result must fit the usage
+    that ``allocation_plan`` was admitted under, or the plan was made with numbers that do not describe this process.
+
+    Reference: ulacache/storage/capacity.py:160-202."""
+    values = (native_device_bytes, native_payload_bytes, replacement_device_bytes, replacement_host_bytes, native_host_bytes)
+    if any(type(v) is not int or v < 0 for v in values):
+        raise ValueError("Byte charges are non-negative integers")
+    if native_payload_bytes > native_device_bytes:
+        raise ValueError("The replaced payload is part of the native device charge")
+    usage = CacheMemoryUsage(native_device_bytes - native_payload_bytes + replacement_device_bytes,
+                             native_host_bytes + replacement_host_bytes)
+    if usage.device_bytes > allocation_plan.usage.device_bytes or usage.host_bytes > allocation_plan.usage.host_bytes:
+        raise ValueError("Native plus replacement charges exceed the usage the allocation plan declared")
+    if not allocation_plan.budget.contains(allocation_plan.usage):
+        raise ValueError("The allocation plan no longer fits its budget")
+    return usage
+
+
+def residency_workspace_bytes(plan_capacity: int, groups: int, device_slots: int) -> dict:
+    """Host-tier transaction workspace of ``groups`` residency groups: the shared plan arrays (five int32 words per
+    plan item plus the new / promote / candidate lists: 32 bytes per item), and per group its expiry list (bounded by
+    the device slots) and counters."""
+    if min(plan_capacity, groups, device_slots) < 1:
+        raise ValueError("Workspace dimensions are positive")
+    fixed = 32 * plan_capacity + 56 * groups
+    expiry = 4 * groups * min(plan_capacity, device_slots)
+    return dict(fixed_bytes=fixed, expiry_bytes=expiry, total_bytes=fixed + expiry)
+
+
 def kv_token_bytes(*, record_bytes: int, layers: int, index_layers: int = 0, metadata_groups: int = 0) -> int:
     """Bytes one resident token costs in a tier: its records in every layer, its share of the
     index pages, and the per-slot metadata of every residency group."""
