@@ -278,3 +278,42 @@ def test_receiver_rooms_lease_destinations_until_completion():
     rx.logical_pages_freed(pages + [9999], transport_quiesced=True)
     assert rx.metadata_inventory()["pending_rooms"] == 0 and len(audits) == 2
     cache.close()
+
+
+def test_index_records_ride_under_the_same_lease():
+    from ulacache_b200.tools.snapshot.cache_io import read_index_records
+    from ulacache_b200.transfer.index_pages import PAGE_BYTES
+    from ulacache_b200.transfer.receive_window import IndexStagedReceiveWindow
+
+    cache = _cache(device_pages=4, host_pages=8)
+    window = IndexStagedReceiveWindow(cache, record_capacity=256, ranks=2, rank=1)
+    target = torch.zeros(16, PAGE_BYTES, dtype=torch.uint8)          # this rank's Index pages of one layer
+    draft = torch.zeros(32, PAGE_BYTES, dtype=torch.uint8)           # a replicated draft Index
+    reg = window.add_index_page_banks("target", [target])
+    window.add_index_page_banks("draft", [draft], replicated=True)
+    with pytest.raises(ValueError):
+        window.add_index_page_banks("target", [target])
+    with pytest.raises(ValueError):
+        window.add_index_page_banks("odd", [torch.zeros(100, dtype=torch.uint8)])
+    assert reg()[0][2] == PAGE_BYTES
+    ids = cache.alloc(256)                                           # four pages: logical pages 1..4
+    window.reserve("room", ids[:192], record_count=150)
+    src = window.staging_rows("room")
+    g = torch.Generator().manual_seed(0)
+    for name in ("target", "draft"):
+        st = window._index_banks[name]["staging"]
+        st.copy_(torch.randint(0, 255, st.shape, dtype=torch.uint8, generator=g))
+    staged = {n: read_index_records(window._index_banks[n]["staging"][0], src) for n in ("target", "draft")}
+    assert window.publish("room") == 150
+    rows = ids[:150].long()
+    page = rows // 64
+    mine = (page % 2 == 1) & (rows >= 2 * 64)                        # this rank's stripe, padding page excluded
+    local = (page // 2) * 64 + rows % 64
+    assert torch.equal(read_index_records(target, local[mine]), staged["target"][mine])
+    assert int(mine.sum()) > 0 and window.memory_inventory()["published_index_records"] == int(mine.sum()) + int((rows >= 64).sum())
+    everyone = rows >= 64
+    assert torch.equal(read_index_records(draft, rows[everyone]), staged["draft"][everyone])
+    untouched = torch.ones(16 * 64, dtype=torch.bool)
+    untouched[local[mine]] = False
+    assert int(read_index_records(target, untouched.nonzero().flatten()).sum()) == 0
+    cache.close()

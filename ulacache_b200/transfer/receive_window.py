@@ -347,3 +347,77 @@ class StagedReceiveWindow:
             published_records=self.published_records,
             pinned=self.pinned,
         )
+
+
+class IndexStagedReceiveWindow(StagedReceiveWindow):
+    """A staged window that also carries the request's Index records under the same lease.  Index records keep
+    their stable addresses (owner-local record = function of the logical id): only the KV records go through the
+    residency directory.  The sender writes native Index pages (64 keys of 128 bytes, then 64 scales of 4) into the
+    window's Index staging; publication copies the records THIS rank owns into the bound page banks.
+
+    Reference: ulacache/transfer/owner_index_receive.py:12-151 (Index page banks under the KV receive lease)."""
+
+    def __init__(self, cache, *, ranks: int = 1, rank: int = 0, **kw):
+        super().__init__(cache, **kw)
+        if type(ranks) is not int or ranks < 1 or not 0 <= rank < ranks:
+            raise ValueError("Index ownership needs a positive owner count and a rank inside it")
+        self.ranks, self.rank = ranks, rank
+        self._index_banks: Dict[str, dict] = {}
+        self.published_index_records = 0
+
+    def add_index_page_banks(self, name: str, destinations, *, replicated: bool = False):
+        """``destinations``: uint8 page pools (whole 8448-byte pages), one per Index layer.  ``replicated``: every
+        rank keeps all records (a draft model's Index) instead of only its stripe."""
+        import torch
+
+        from .index_pages import PAGE_BYTES
+
+        if self._frozen or self._pending:
+            raise RuntimeError("banks are fixed once addresses were handed out or a transfer was reserved")
+        if not isinstance(name, str) or not name or name in self._index_banks or name in self._sidecars \
+                or type(replicated) is not bool:
+            raise ValueError("an Index bank needs a unique name and an explicit ownership")
+        banks = list(destinations)
+        if not banks or any(not isinstance(b, torch.Tensor) or b.dtype != torch.uint8 or not b.is_contiguous()
+                            or b.numel() == 0 or b.numel() % PAGE_BYTES for b in banks):
+            raise ValueError("Index banks are contiguous uint8 tensors of whole pages")
+        pages = self.record_capacity // PAGE
+        staging = self._host((len(banks), pages, PAGE_BYTES))
+        self._index_banks[name] = dict(staging=staging, destinations=banks, replicated=replicated)
+
+        def registration():
+            self._frozen = True
+            return [(staging[l].data_ptr(), staging[l].numel(), PAGE_BYTES) for l in range(staging.shape[0])]
+
+        return registration
+
+    def validate_extra_destinations(self, rows):
+        from .index_pages import PAGE_BYTES, owner_local_record
+
+        if not rows.numel() or not self._index_banks:
+            return
+        for bank in self._index_banks.values():
+            ranks = 1 if bank["replicated"] else self.ranks
+            last = max(owner_local_record(int(r), ranks)[1] for r in (rows.max(), rows.min()))
+            if any((last // PAGE + 1) * PAGE_BYTES > d.numel() for d in bank["destinations"]):
+                raise ValueError("an Index bank is too small for these records")
+
+    def publish_extra_banks(self, item):
+        from .index_pages import plan_index_record_copies, publish_index_records
+
+        rows, src = item["rows"].tolist(), item["source_rows"].tolist()
+        for bank in self._index_banks.values():
+            ranks, rank = (1, 0) if bank["replicated"] else (self.ranks, self.rank)
+            keep = [(r, s) for r, s in zip(rows, src) if r >= ranks * PAGE]          # the first page is padding
+            plan = plan_index_record_copies([r for r, _ in keep], [s for _, s in keep], ranks=ranks, rank=rank)
+            for layer, dest in enumerate(bank["destinations"]):
+                staged = bank["staging"][layer]
+                self.published_index_records += publish_index_records(
+                    staged.to(dest.device) if dest.device.type != "cpu" else staged, dest, plan, transport_quiesced=True)
+
+    def memory_inventory(self) -> dict:
+        out = super().memory_inventory()
+        out["cpu_receive_bytes"] += sum(b["staging"].numel() for b in self._index_banks.values())
+        out["index_banks"] = sum(len(b["destinations"]) for b in self._index_banks.values())
+        out["published_index_records"] = self.published_index_records
+        return out
