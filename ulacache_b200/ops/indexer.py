@@ -109,3 +109,61 @@ def select_topk(logits, k, page_table, *, n_q, ranks=1, rank=0, with_values=Fals
     ids = cols_to_ids(cols, page_table, n_q=n_q, ranks=ranks, rank=rank)
     ids = torch.where(torch.isfinite(vals), ids, torch.full_like(ids, -1))
     return (ids, vals) if with_values else ids
+
+
+def index_ragged_gather_reference(pools, page_table, lengths):
+    """PyTorch statement of :func:`index_ragged_gather`: ``pools`` = one uint8 [pages, 8448] tensor per owner."""
+    import torch
+
+    ranks = len(pools)
+    keys, scales = [], []
+    for q in range(page_table.shape[0]):
+        n = int(lengths[q])
+        t = torch.arange(n, device=page_table.device)
+        col = t // 64
+        page = torch.where(col < page_table.shape[1], page_table[q, col.clamp(max=page_table.shape[1] - 1)].long(),
+                           torch.zeros_like(col))
+        k = torch.zeros((n, 128), dtype=torch.uint8, device=page_table.device)
+        s = torch.zeros(n, dtype=torch.float32, device=page_table.device)
+        for r in range(ranks):
+            m = (page > 0) & (page % ranks == r) & (page // ranks < pools[r].shape[0])
+            if bool(m.any()):
+                rows = pools[r][(page[m] // ranks)]
+                off = (t[m] % 64)
+                k[m] = torch.gather(rows, 1, (off * 128)[:, None] + torch.arange(128, device=rows.device))
+                sb = torch.gather(rows, 1, (8192 + off * 4)[:, None] + torch.arange(4, device=rows.device))
+                s[m] = sb.contiguous().view(torch.float32).reshape(-1)
+        keys.append(k)
+        scales.append(s)
+    return torch.cat(keys), torch.cat(scales)
+
+
+def index_ragged_gather(pool_ptrs, page_table, lengths, *, pool_pages: int, status=None):
+    """Dense (keys uint8 [sum(lengths), 128], scales fp32 [sum(lengths)]) of every query's causal prefix, read from
+    an Index striped over ``len(pool_ptrs)`` owners (logical page p on owner p % ranks, its page p // ranks).
+    ``pool_ptrs``: base address of this layer's page pool on every owner (local or peer memory; tensors are
+    accepted too); ``page_table`` int32 [queries, pages] logical page numbers (<= 0 = padding);
+    ``lengths`` int32 [queries].  The prefix sums and the total are taken on the host (a prefill chunk is eager)."""
+    import ctypes as C
+
+    import torch
+
+    ptrs = [int(p.data_ptr()) if hasattr(p, "data_ptr") else int(p) for p in pool_ptrs]
+    lengths = lengths.to(torch.int32).contiguous()
+    page_table = page_table.to(torch.int32)
+    if page_table.stride(1) != 1:
+        page_table = page_table.contiguous()
+    offsets = (torch.cumsum(lengths, 0) - lengths).to(torch.int32)
+    total = int(lengths.sum())
+    longest = int(lengths.max()) if lengths.numel() else 0
+    keys = torch.empty((total, 128), dtype=torch.uint8, device=page_table.device)
+    scales = torch.empty(total, dtype=torch.float32, device=page_table.device)
+    if total == 0:
+        return keys, scales
+    arr = (C.c_void_p * len(ptrs))(*ptrs)
+    N.check(N.cuda().ulc_index_ragged_gather(arr, C.c_int(len(ptrs)), C.c_int(pool_pages), N.ptr(page_table),
+                                             C.c_longlong(page_table.stride(0)), C.c_int(page_table.shape[1]),
+                                             N.ptr(lengths), N.ptr(offsets), C.c_int(lengths.numel()), C.c_int(longest),
+                                             C.c_int(total), N.ptr(keys), N.ptr(scales), N.ptr(status), N.stream()),
+            "index_ragged_gather")
+    return keys, scales
