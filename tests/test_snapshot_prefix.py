@@ -57,6 +57,10 @@ def test_prefix_round_trip_through_banks_and_stripes(tmp_path):
             assert raw == want.numpy().tobytes(), (owner, plane)
     with pytest.raises(ValueError):
         stripe_prefix(striped, str(tmp_path / "again"), 2)            # already striped
+    from ulacache_b200.tools import cli
+
+    assert cli.main(["stripe", path, "--to", str(tmp_path / "by_cli"), "--owners", "3", "--chunk-rows", "64"]) == 0
+    assert SnapshotReader(str(tmp_path / "by_cli")).layout.owners == 3 and cli.main(["verify", str(tmp_path / "by_cli")]) == 0
     with pytest.raises(FileExistsError):
         stripe_prefix(path, striped, 4)
 

@@ -1,4 +1,5 @@
-"""``ulacache-kv-snapshot inspect|verify|commit <dir>`` (also ``python -m ulacache_b200.tools.cli``).
+"""``ulacache-kv-snapshot inspect|verify|commit <dir>`` and ``stripe <dir> --to <dir> --owners N`` (also
+``python -m ulacache_b200.tools.cli``).  ``stripe`` converts a one-owner, one-request prefix snapshot into owner stripes.
 
 Reference: ulacache/tools/cli.py:8-37.
 """
@@ -13,9 +14,20 @@ def main(argv=None) -> int:
     from .snapshot.format import SnapshotReader, finalize_snapshot
 
     ap = argparse.ArgumentParser(prog="ulacache-kv-snapshot")
-    ap.add_argument("command", choices=["inspect", "verify", "commit"])
+    ap.add_argument("command", choices=["inspect", "verify", "commit", "stripe"])
     ap.add_argument("path")
+    ap.add_argument("--to", default="", help="stripe: the directory to create")
+    ap.add_argument("--owners", type=int, default=0, help="stripe: number of owners")
+    ap.add_argument("--chunk-rows", type=int, default=65536, help="stripe: rows of one plane held in memory at a time")
     args = ap.parse_args(argv)
+    if args.command == "stripe":
+        from .snapshot.prefix import stripe_prefix
+
+        if not args.to or args.owners < 1:
+            ap.error("stripe needs --to DIR and --owners N")
+        commit = stripe_prefix(args.path, args.to, args.owners, chunk_rows=args.chunk_rows)
+        print(json.dumps({"striped": True, "owners": len(commit["owners"]), "path": args.to}))
+        return 0
     if args.command == "commit":
         commit = finalize_snapshot(args.path)
         print(json.dumps({"committed": True, "owners": len(commit["owners"]), "requests": commit["request_count"]}))
