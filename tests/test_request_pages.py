@@ -141,3 +141,52 @@ def test_fresh_bindings_are_settled_before_a_boundary_publication():
     pub.record_completed_bindings([(3, 2), (4, 3)])
     pub.publish([(0, 1)])                                       # keeps the fresh bindings
     assert pub.device_map.tolist() == [1, -1, -1, 2, 3, -1, -1, -1]
+
+
+def test_request_address_runtime_brackets_forwards_and_guards_page_moves():
+    from ulacache_b200.cache.request_access import RequestAddressRuntime
+    from ulacache_b200.cache.request_storage import RequestTier
+
+    tier = RequestTier(layers=2, device_pages=8, host_pages=8, logical_pages=32, record_bytes=16, device="cpu",
+                       pin_host=False, topk=16)
+    rt = RequestAddressRuntime(device="cpu")
+    tier.bind_runtime(rt)
+    tier.admit(1, 3 * 64)
+    tier.admit(2, 4 * 64)
+    rt.begin_forward()
+    with pytest.raises(RuntimeError):
+        rt.begin_forward()
+    with pytest.raises(RuntimeError):                          # request 3 needs request 1's pages: readers are in flight
+        tier.admit(3, 3 * 64)
+    assert 3 not in tier.pool.pages_of or not tier.pool.pages_of[3]
+    rt.finish_forward()
+    with pytest.raises(RuntimeError):
+        rt.finish_forward()
+    assert tier.admit(3, 3 * 64) > 0 and rt.boundary_waits >= 1 and rt.forwards == 1
+    rt.begin_prefill()
+    rt.finish_prefill()
+    assert rt.forwards == 2
+
+    class Publication:                                         # peers that have not published their phase yet
+        def __init__(self):
+            self.published, self.free = [], False
+
+        def publish(self, domain, phase):
+            self.published.append((domain, phase))
+
+        def may_move_records(self, domain):
+            return self.free
+
+    pub = Publication()
+    grouped = RequestAddressRuntime(device="cpu", publication=pub, domain=2)
+    other = RequestTier(layers=1, device_pages=4, host_pages=4, logical_pages=16, record_bytes=16, device="cpu", pin_host=False)
+    other.bind_runtime(grouped)
+    grouped.begin_forward()
+    grouped.finish_forward()
+    assert pub.published == [(2, 1)] and grouped.readers_retired(other) is False
+    pub.free = True
+    assert grouped.readers_retired(other) is True
+    wrong = RequestTier(layers=1, device_pages=4, host_pages=4, logical_pages=16, record_bytes=16, device="cpu", pin_host=False)
+    wrong.page_map = wrong.page_map.to(torch.int64)
+    with pytest.raises(ValueError):
+        RequestAddressRuntime(device="cpu").validate(wrong)
