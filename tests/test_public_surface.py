@@ -358,3 +358,17 @@ def test_payload_replacement_pricing_and_workspace_bytes():
     assert residency_workspace_bytes(4096, 2, 100)["expiry_bytes"] == 800
     with pytest.raises(ValueError):
         residency_workspace_bytes(0, 1, 1)
+
+
+def test_capacity_experiment_prints_the_history_audit():
+    from ulacache_b200.experiments.capacity import history_audit
+
+    audit = history_audit(device_gb=72.0, host_gb=128.0, ranks=8, layers=61, requests=512, max_context=131072)
+    part, space = audit["required_partitions"][0], audit["request_namespaces"][0]
+    assert part["record_owner_count"] == 8 and part["reserved_logical_record_count"] == 512
+    assert space["usable_history_token_slots"] == min(space["cold_storage_history_token_slots"],
+                                                      space["native_allocator_usable_token_slots"],
+                                                      space["request_address_token_slots"])
+    assert audit["total_usable_history_token_slots"] > 30_000_000
+    tight = history_audit(device_gb=72.0, host_gb=128.0, ranks=8, layers=61, requests=8, max_context=4096)
+    assert tight["total_usable_history_token_slots"] == 8 * 4096          # addressing binds, not memory

@@ -55,6 +55,22 @@ def organisations(*, device_gb: float, host_gb: float, ranks: int, layers: int, 
     return out
 
 
+def history_audit(*, device_gb: float, host_gb: float, ranks: int, layers: int, requests: int, max_context: int) -> dict:
+    """The pooled organisation as an addressable-history audit: one request namespace, one KV partition whose owners
+    are the ranks' planned tiers, bounded by the allocator (what was planned) and by request addressing."""
+    from ..storage.capacity import (RecordOwnerCapacity, RequestNamespaceCapacityBounds, RequiredCachePartitionCapacity,
+                                    addressable_tokens_per_owner, calculate_addressable_history_capacity)
+    from ..storage.layout import StorageLayout
+
+    org = organisations(device_gb=device_gb, host_gb=host_gb, ranks=ranks, layers=layers, requests_per_rank=max(1, requests // ranks))
+    dev, host = org["pooled"]["device_tokens_per_rank"], org["pooled"]["host_tokens_per_rank"]
+    owners = tuple(RecordOwnerCapacity(r, dev, host) for r in range(ranks))
+    part = RequiredCachePartitionCapacity(0, "kv", StorageLayout(name="mla.scaled656"), owners, reserved_logical_record_count=64 * ranks)
+    addressable = addressable_tokens_per_owner(maximum_requests=requests, maximum_context_tokens=max_context, owners=ranks) * ranks
+    bounds = RequestNamespaceCapacityBounds(0, (dev + host) * ranks, addressable)
+    return calculate_addressable_history_capacity([part], [bounds])
+
+
 def from_audit(directory: str):
     files = sorted(glob.glob(os.path.join(directory, "rank*.json")))
     if not files:
@@ -76,7 +92,15 @@ def main():
     ap.add_argument("--layers", type=int, default=61)
     ap.add_argument("--requests-per-rank", type=int, default=64)
     ap.add_argument("--audit-dir", default="")
+    ap.add_argument("--history-audit", action="store_true",
+                    help="print the pooled organisation as an addressable-history audit (partitions, owners, bounds)")
+    ap.add_argument("--max-context", type=int, default=131072)
     args = ap.parse_args()
+    if args.history_audit:
+        print(json.dumps({"experiment": "capacity_history_audit",
+                          **history_audit(device_gb=args.device_gb, host_gb=args.host_gb, ranks=args.ranks, layers=args.layers,
+                                          requests=args.requests_per_rank * args.ranks, max_context=args.max_context)}))
+        return
     if args.audit_dir:
         print(json.dumps({"experiment": "capacity_audit", **from_audit(args.audit_dir)}))
         return
